@@ -78,7 +78,7 @@ class KVCacheManager:
                 shape = (2, need.kv_heads, page_size, need.head_dim) if same else \
                     (need.kv_heads * page_size * (need.head_dim + value_columns(need)),)
                 data = torch.zeros((layers, num_pages + 1, *shape), dtype=dtype, device=device)
-            self.groups.append(CacheGroup(need, layers, GroupTables(num_pages, page_size, need.window), data))
+            self.groups.append(CacheGroup(need, layers, GroupTables(num_pages, page_size, need.window, need.keep_first), data))
         self.states: List[Optional[torch.Tensor]] = []
         self.state_needs = list(states)
         for need in states:

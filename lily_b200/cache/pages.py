@@ -11,7 +11,8 @@ with the device tensors.
   captured decode graph can point at it, lily/mem_cache/memory_pool.py:21-30).
 * ``BlockTable``: for one request in one cache group, the page that holds each run of
   ``page_size`` positions.  In a group with a window, pages wholly behind the window are
-  given back while the request lives; their entries become 0 and are never read again.
+  given back while the request lives; their entries become 0 and are never read again.  A group
+  whose window also keeps a request's first positions holds on to the pages those lie in.
 """
 
 from __future__ import annotations
@@ -100,7 +101,7 @@ class BlockTable:
         self.stamp = next(BlockTable._stamps)
 
     def live_pages(self) -> List[int]:
-        return [p for p in self.pages[self.first_live:] if p]
+        return [p for p in self.pages if p]            # kept first pages may lie before ``first_live``
 
 
 def pages_for(length: int, page_size: int) -> int:
@@ -110,10 +111,11 @@ def pages_for(length: int, page_size: int) -> int:
 class GroupTables:
     """All block tables of one cache group, over one page pool."""
 
-    def __init__(self, num_pages: int, page_size: int, window: Optional[int] = None):
+    def __init__(self, num_pages: int, page_size: int, window: Optional[int] = None, keep_first: int = 0):
         self.pool = PagePool(num_pages)
         self.page_size = page_size
         self.window = window
+        self.kept_pages = pages_for(max(0, int(keep_first)), page_size) if window is not None else 0
         self.tables: Dict[int, BlockTable] = {}
 
     def open(self, slot: int) -> None:
@@ -140,8 +142,9 @@ class GroupTables:
         t = self.tables[slot]
         first_needed = max(0, seq_len - self.window + 1) // self.page_size
         first_needed = min(first_needed, len(t.pages))
-        gone = [p for p in t.pages[t.first_live:first_needed] if p]
-        for i in range(t.first_live, first_needed):
+        start = max(t.first_live, self.kept_pages)          # the pages of the first positions are never given back
+        gone = [p for p in t.pages[start:first_needed] if p]
+        for i in range(start, first_needed):
             t.pages[i] = 0
         if first_needed > t.first_live:
             t.touch()
@@ -151,4 +154,4 @@ class GroupTables:
 
     def close(self, slot: int) -> None:
         t = self.tables.pop(slot)
-        self.pool.free(t.live_pages())
+        self.pool.free([p for p in t.pages if p])

@@ -48,11 +48,17 @@ def _require(d: Dict[str, Any], key: str, kind=int):
 class RopeScaling:
     """Frequency scaling of the rotary table (lily/layers/rotary.py:90-119,196-207)."""
 
-    rope_type: str = "default"          # "default" | "llama3"
+    rope_type: str = "default"          # "default" | "llama3" | "yarn"
     factor: float = 1.0
     low_freq_factor: float = 1.0
     high_freq_factor: float = 1.0
     original_max_position_embeddings: int = 0
+    # "yarn": waves that make more than ``fast_turns`` turns over the original length keep their frequency, those that
+    # make fewer than ``slow_turns`` are slowed by ``factor``, a linear ramp over the feature index in between; the
+    # tables are stretched by ``table_stretch_slope * ln(factor) + 1``
+    fast_turns: float = 32.0
+    slow_turns: float = 1.0
+    table_stretch_slope: float = 0.1
 
     @classmethod
     def from_dict(cls, d: Optional[Dict[str, Any]]) -> "RopeScaling":

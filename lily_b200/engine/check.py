@@ -45,7 +45,8 @@ def check_tables(cache, slots_and_lengths: Sequence[tuple]) -> None:
                 _fail(f"slot {slot}, group {g}: {len(pages)} pages of {page} do not cover {after} positions")
             # the oldest position any query of this step may look at
             first_read = 0 if window is None else max(0, before + 1 - window)
-            for i in range(first_read // page, -(-after // page)):
+            kept = min(tables.kept_pages, -(-after // page))                 # pages of the first positions a window keeps
+            for i in list(range(kept)) + list(range(max(kept, first_read // page), -(-after // page))):
                 if not (1 <= pages[i] <= cache.num_pages):
                     _fail(f"slot {slot}, group {g}: page id {pages[i]} at table entry {i}, whose positions {i * page} to "
                           f"{(i + 1) * page - 1} this step reads or writes (the pool has pages 1 to {cache.num_pages})")

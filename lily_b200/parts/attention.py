@@ -20,12 +20,13 @@ lily/layers/attention/triton_backend.py:110-141 (cache write before attention).
 
 from __future__ import annotations
 
+import dataclasses
 from dataclasses import dataclass
 from typing import Any, Dict, Optional, Tuple
 
 import torch
 
-from lily_b200.parts.base import BuildContext, CacheNeed, Mixer, TensorSpec, build_part, register_part
+from lily_b200.parts.base import BuildContext, CacheNeed, Mixer, StateNeed, TensorSpec, build_part, register_part
 
 
 @dataclass(frozen=True)
@@ -45,14 +46,23 @@ class AttentionSpec:
     softcap: Optional[float] = None       # scores become softcap * tanh(score * scale / softcap)
     out_gate: bool = False                # heads * sigmoid(W_g x) before the output projection
     # names of the tensors under the part's prefix: q, k, v, o (and g) weights; None: "<x>_proj.weight"
+    # (the convolution's weights: roles "q_conv", "k_conv", "v_conv", default "<x>_proj.conv")
     names: Optional[Tuple[Tuple[str, str], ...]] = None
+    keep_first: int = 0                   # with a window: key j is also seen when j < keep_first
+    conv_taps: int = 0                    # 0: none; n: y_t = sum_j w[:, j] u_(t - n + 1 + j) on each channel of q, k and v
 
     @property
     def value_dim(self) -> int:
         return self.v_head_dim or self.head_dim
 
     def name(self, role: str) -> str:
-        return dict(self.names or ()).get(role, f"{role}_proj.weight")
+        default = f"{role[0]}_proj.conv" if role.endswith("_conv") else f"{role}_proj.weight"
+        return dict(self.names or ()).get(role, default)
+
+    @property
+    def projected(self) -> int:
+        """Columns of the stacked q, k and v projections."""
+        return (self.num_heads + self.num_kv_heads) * self.head_dim + self.num_kv_heads * self.value_dim
 
 
 @dataclass
@@ -87,12 +97,24 @@ class Attention(Mixer):
         self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.q_gain = self.k_gain = self.w_g = None
         if spec.value_dim != spec.head_dim and (spec.bias or spec.qk_norm):
             raise ValueError("a value head size of its own comes without biases and q/k norms")
+        if spec.keep_first and not spec.window:
+            raise ValueError("first positions are kept in sight only beside a window")
+        if spec.conv_taps < 0 or (spec.conv_taps and spec.bias):
+            raise ValueError("the short convolution has at least one tap and comes without biases")
+        self.conv_w = None
 
     # ---- what it needs ----------------------------------------------------------
 
     def cache_need(self) -> CacheNeed:
         s = self.spec
-        return CacheNeed(s.num_kv_heads, s.head_dim, s.window, None if s.value_dim == s.head_dim else s.value_dim)
+        return CacheNeed(s.num_kv_heads, s.head_dim, s.window, None if s.value_dim == s.head_dim else s.value_dim,
+                         keep_first=int(s.keep_first) if s.window else 0)
+
+    def state_need(self) -> Optional[StateNeed]:
+        s = self.spec
+        if s.conv_taps > 1:
+            return StateNeed(((s.conv_taps - 1) * s.projected,), torch.float32)      # the last projected rows, oldest first
+        return None
 
     def tensors(self) -> Dict[str, TensorSpec]:
         s, p = self.spec, self.prefix
@@ -104,6 +126,10 @@ class Attention(Mixer):
                f"{p}.{s.name('o')}": TensorSpec((s.hidden_size, heads_out))}
         if s.out_gate:
             out[f"{p}.{s.name('g')}"] = TensorSpec((heads_out, s.hidden_size))
+        if s.conv_taps:
+            out.update({f"{p}.{s.name('q_conv')}": TensorSpec((q, s.conv_taps), role="vector", init="normal"),
+                        f"{p}.{s.name('k_conv')}": TensorSpec((kv, s.conv_taps), role="vector", init="normal"),
+                        f"{p}.{s.name('v_conv')}": TensorSpec((s.num_kv_heads * s.value_dim, s.conv_taps), role="vector", init="normal")})
         if s.bias:
             out.update({f"{p}.q_proj.bias": TensorSpec((q,), role="matrix"),
                         f"{p}.k_proj.bias": TensorSpec((kv,), role="matrix"),
@@ -132,6 +158,12 @@ class Attention(Mixer):
         self.w_o = get(f"{p}.{s.name('o')}").contiguous()
         if s.out_gate:
             self.w_g = get(f"{p}.{s.name('g')}").contiguous()
+        if s.conv_taps:
+            wc = [get(f"{p}.{s.name(r)}").float() for r in ("q_conv", "k_conv", "v_conv")]
+            if self.position is not None and getattr(self.position, "interleaved", False):
+                wc[0] = wc[0].view(s.num_heads, s.head_dim, -1)[:, order].reshape(q, -1)
+                wc[1] = wc[1].view(s.num_kv_heads, s.head_dim, -1)[:, order].reshape(kv, -1)
+            self.conv_w = torch.cat(wc).contiguous()                       # [q | k | v channels, taps], float32
         if s.bias:
             self.b_qkv = torch.cat([get(f"{p}.{n}_proj.bias") for n in "qkv"]).contiguous()
             self.b_o = get(f"{p}.o_proj.bias").contiguous()
@@ -147,9 +179,12 @@ class Attention(Mixer):
         """How this step's attention runs for this mixer's sizes in cache group ``group``; made once a step and
         shared by every layer with the same sizes (``batch.plan``)."""
         s, ops = self.spec, self.ctx.ops
-        key = ("attention", group, s.num_heads, s.num_kv_heads, s.head_dim, dtype, page, s.value_dim, bool(s.softcap))
+        key = ("attention", group, s.num_heads, s.num_kv_heads, s.head_dim, dtype, page, s.value_dim, bool(s.softcap),
+               bool(s.keep_first), bool(s.conv_taps))
         sized = {} if s.value_dim == s.head_dim else {"dv": s.value_dim}      # options go to the kernels' faces only
         capped = {"softcap": s.softcap} if s.softcap else {}                  # where the spec sets them
+        if s.keep_first:
+            sized = dict(sized, keep_first=int(s.keep_first))
 
         def make(b):
             nd = b.num_decode
@@ -158,6 +193,8 @@ class Attention(Mixer):
             if decode != ops.plan_decode_attention(dtype, nd, s.num_heads, s.num_kv_heads, s.head_dim, b.max_decode_len,
                                                    even=not b.decode_even, **sized):
                 b.even_asked = True              # a captured step with this plan serves batches of this kind only
+            if s.conv_taps and decode.fused:
+                decode = dataclasses.replace(decode, fused=False)     # the convolution stands between projection and rotation
             rows = tiles = None
             if b.num_requests > nd:
                 rows = ops.prefill_tile_rows(dtype, s.head_dim, page, b.num_tokens - nd, **capped, **sized)
@@ -171,9 +208,17 @@ class Attention(Mixer):
         dv = s.value_dim
         sized = {} if dv == s.head_dim else {"dv": dv}
         capped = {"softcap": s.softcap} if s.softcap else {}
+        kept = {"keep_first": int(s.keep_first)} if s.keep_first else {}
         table = batch.block_tables[cache.group]
         plan = self._plan(batch, cache.group, cache.data.dtype, page)
-        qkv = ops.linear_auto(x, self.w_qkv, self.b_qkv)
+        if s.conv_taps:
+            chunk = ops.SSM_CHUNK
+            chunk_req, chunk_start = batch.plan(("token_chunks", chunk),
+                                                lambda b: ops.token_chunks(b.h_new_lens, chunk, b.token_ids.device))
+            qkv = ops.causal_conv(ops.linear(x, self.w_qkv), 0, s.projected, self.conv_w, None, state, 0, chunk_req,
+                                  chunk_start, batch.cu_seqlens, batch.slots, chunk, activation="none")
+        else:
+            qkv = ops.linear_auto(x, self.w_qkv, self.b_qkv)
         cos, sin = self.position.tables() if self.position is not None else (None, None)
         rotary_dim = self.position.rotary_dim if self.position is not None else 0
         nd, dec = batch.num_decode, plan.decode
@@ -195,12 +240,12 @@ class Attention(Mixer):
         if nd:
             ops.attention_decode(q[:nd], cache.data, table, batch.seq_lens, out[:nd], scratch, dec.splits,
                                  s.num_heads, s.num_kv_heads, s.head_dim, page, self.scale, s.window, stages=dec.stages,
-                                 **capped, **sized)
+                                 **capped, **sized, **kept)
         if batch.num_requests > nd:
             tile_req, tile_start = plan.tiles
             ops.attention_prefill(q, cache.data, table, batch.cu_seqlens, batch.prefix_lens, tile_req, tile_start,
                                   out, s.num_heads, s.num_kv_heads, s.head_dim, page, self.scale, s.window,
-                                  tile_rows=plan.tile_rows, **capped, **sized)
+                                  tile_rows=plan.tile_rows, **capped, **sized, **kept)
         if gate is not None:
             ops.sigmoid_gate(out, gate)
         return ops.linear_auto(out, self.w_o, self.b_o)

@@ -68,7 +68,8 @@ class TensorSpec:
 class CacheNeed:
     """Paged keys and values.  Layers whose needs are equal share a cache group
     (one pool of pages and one block table per request); ``window`` None keeps all keys,
-    an integer keeps the last ``window`` of them and lets older pages go."""
+    an integer keeps the last ``window`` of them and lets older pages go, except those that hold
+    any of a request's first ``keep_first`` positions, which every later query still sees."""
 
     kv_heads: int
     head_dim: int
@@ -76,6 +77,7 @@ class CacheNeed:
     v_head_dim: Optional[int] = None     # the values' head size where it differs from the keys' (None: head_dim)
     values_in_keys: bool = False         # the values are columns of the key rows themselves (a cached latent that serves
                                          # as both): a page holds keys only
+    keep_first: int = 0                  # with a window: the request's first positions stay visible (and cached) for good
 
 
 @dataclass(frozen=True)
@@ -201,7 +203,7 @@ def _load_builtin_parts() -> None:
     global _BUILTINS
     if not _BUILTINS:
         _BUILTINS = True
-        from lily_b200.parts import attention, block, experts, latent_attention, mlp, norm, rope, ssm, wkv  # noqa: F401
+        from lily_b200.parts import attention, block, diff_attention, experts, latent_attention, mlp, norm, rope, ssm, wkv  # noqa: F401
 
 
 # --------------------------------------------------------------------------- model description

@@ -1,5 +1,6 @@
 """Block arrangements.  The pre-norm block: ``r += mixer(norm_in(r)); r += feed_forward(norm_post(r))``; the parallel
-block (``ParallelBlockSpec``): one norm, several mixers and the feed-forward side by side on its output.
+block (``ParallelBlockSpec``): one norm, several mixers and the feed-forward side by side on its output; the sandwich
+block (``SandwichBlockSpec``): a norm on both sides of each sublayer and a multiplier on what enters the stream.
 
 The residual stream ``r`` is float32 and updated in place; each add is fused into the norm that
 follows it, so a block receives the pending delta of the block before it and returns its own
@@ -12,6 +13,7 @@ from dataclasses import dataclass
 from typing import Any, Dict, Tuple
 
 from lily_b200.parts.base import Block, BlockSpec, BuildContext, RunSlots, TensorSpec, build_part, register_part
+from lily_b200.parts.norm import NormedDelta
 
 
 @register_part("block", "prenorm")
@@ -113,3 +115,61 @@ class ParallelBlock(Block):
             return (outs[0], f) if f is not None else outs[0]          # summed in float32 by the next residual add
         # float32, as one plane of partial sums: the next norm adds it into the residual stream
         return self.ctx.ops.normed_mean(outs, self.gains, self.spec.eps, add=f)
+
+
+@dataclass(frozen=True)
+class SandwichBlockSpec:
+    """A norm ahead of and behind each sublayer: ``r += mult * norm_1b(mixer(norm_1(r)))``, then, where the block has a
+    feed-forward, ``r += mult * norm_2b(ff(norm_2(r)))``.  The norm behind a sublayer and the add are folded into the
+    pass of the norm that comes next (``NormedDelta``), in this block or in the one after it."""
+
+    prefix: str
+    mixer: Any
+    feed_forward: Any                         # None: the block ends behind its mixer
+    norm: Any                                 # the spec of all four norms (size, eps, gain naming)
+    mult: float = 1.0
+    kind: str = "sandwich"
+    mixer_name: str = "mix"
+    feed_forward_name: str = "mlp"
+    norm_names: Tuple[str, str, str, str] = ("norm1", "norm1b", "norm2", "norm2b")
+
+
+@register_part("block", "sandwich")
+class SandwichBlock(Block):
+    def __init__(self, spec: SandwichBlockSpec, prefix: str, ctx: BuildContext):
+        self.spec, self.ctx = spec, ctx
+        p = spec.prefix
+        n1, n1b, n2, n2b = spec.norm_names
+        self.norm_in = build_part("norm", spec.norm, f"{p}.{n1}", ctx)
+        self.norm_in_post = build_part("norm", spec.norm, f"{p}.{n1b}", ctx)
+        self.mixer = build_part("mixer", spec.mixer, f"{p}.{spec.mixer_name}", ctx)
+        self.mixers = (self.mixer,)
+        self.parts = (self.norm_in, self.norm_in_post, self.mixer)
+        self.feed_forward = self.norm_ff = self.norm_ff_post = None
+        if spec.feed_forward is not None:
+            self.norm_ff = build_part("norm", spec.norm, f"{p}.{n2}", ctx)
+            self.norm_ff_post = build_part("norm", spec.norm, f"{p}.{n2b}", ctx)
+            self.feed_forward = build_part("feed_forward", spec.feed_forward, f"{p}.{spec.feed_forward_name}", ctx)
+            self.parts += (self.norm_ff, self.norm_ff_post, self.feed_forward)
+        self.post_gains = []
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        out: Dict[str, TensorSpec] = {}
+        for part in self.parts:
+            out.update(part.tensors())
+        return out
+
+    def load(self, get) -> None:
+        for part in self.parts:
+            part.load(get)
+        # the gains of the norms behind the sublayers enter a float32 sum
+        self.post_gains = [n.weight.float().contiguous() for n in (self.norm_in_post, self.norm_ff_post) if n is not None]
+
+    def forward(self, residual, delta, batch, run: RunSlots):
+        eps, mult = self.spec.norm.eps, float(self.spec.mult)
+        h = self.norm_in.forward(residual, delta, delta_bias=run.stream_bias)
+        a = NormedDelta(self.mixer.forward(h, batch, run.caches[0], run.states[0], run.write_cache), self.post_gains[0], eps, mult)
+        if self.feed_forward is None:
+            return a
+        h = self.norm_ff.forward(residual, a)
+        return NormedDelta(self.feed_forward.forward(h, batch), self.post_gains[1], eps, mult)

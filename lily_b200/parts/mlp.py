@@ -80,3 +80,40 @@ class SwiGLU(FeedForward):
         else:
             act = ops.silu_mul(product(x, self.w_gate_up), x.dtype, block=self.block, **how)
         return product(act, self.w_down)
+
+
+@dataclass(frozen=True)
+class DenseMLPSpec:
+    """The plain (ungated) feed-forward ``down(act(up(x)))``, no bias; ``activation``: "relu2" (the square of
+    max(., 0)), "gelu_tanh" or "silu"."""
+
+    hidden_size: int
+    intermediate_size: int
+    kind: str = "dense_mlp"
+    activation: str = "relu2"
+    names: Optional[Tuple[Tuple[str, str], ...]] = None     # names of the up and down weights under the part's prefix
+
+    def name(self, role: str) -> str:
+        return dict(self.names or ()).get(role, f"{role}_proj.weight")
+
+
+@register_part("feed_forward", "dense_mlp")
+class DenseMLP(FeedForward):
+    def __init__(self, spec: DenseMLPSpec, prefix: str, ctx: BuildContext):
+        self.spec, self.prefix, self.ctx = spec, prefix, ctx
+        self.w_up = self.w_down = None
+
+    def tensors(self) -> Dict[str, TensorSpec]:
+        h, i, p, n = self.spec.hidden_size, self.spec.intermediate_size, self.prefix, self.spec.name
+        return {f"{p}.{n('up')}": TensorSpec((i, h)), f"{p}.{n('down')}": TensorSpec((h, i))}
+
+    def load(self, get) -> None:
+        self.w_up = get(f"{self.prefix}.{self.spec.name('up')}").contiguous()
+        self.w_down = get(f"{self.prefix}.{self.spec.name('down')}").contiguous()
+
+    def forward(self, x, batch):
+        ops = self.ctx.ops
+        # the product with the activation in its epilogue where a kernel of that form takes the shape; else the
+        # product (whole, or float32 partial sums for a few tokens) and the activation as a pass of its own
+        act = ops.linear_activation(x, self.w_up, self.spec.activation)
+        return ops.linear_auto(act, self.w_down)

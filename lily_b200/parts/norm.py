@@ -9,9 +9,21 @@ normalised (the final norm before the logits).
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict
+from typing import Any, Dict
 
 from lily_b200.parts.base import BuildContext, Norm, TensorSpec, register_part
+
+
+@dataclass
+class NormedDelta:
+    """A sublayer's output that enters the residual stream as ``mult * (rms(delta) * gain)``, its own root mean
+    square (with ``eps``) taken over the row first (a norm behind the sublayer as well as ahead of it).  A block hands
+    it on as its pending delta; the norm that follows folds it into the stream in the pass in which it normalises."""
+
+    delta: Any                 # [tokens, size] in the compute dtype, or float32 partial sums [splits, tokens, size]
+    gain: Any                  # float32 [size]
+    eps: float
+    mult: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -41,6 +53,12 @@ class RMSNorm(Norm):
     def forward(self, residual, delta=None, delta_bias=None, rows=None, write_residual=True, also=None, out_dtype=None):
         """``delta`` may be a tuple of tensors to be summed; ``delta_bias`` a float32 vector added to every row;
         ``also`` another norm of this kind and size whose output of the same rows is wanted too (returns a pair)."""
+        if isinstance(delta, NormedDelta):
+            if delta_bias is not None or also is not None:
+                raise ValueError("a normalised delta comes alone: no stream vector and no second norm in the same pass")
+            return self.ctx.ops.add_normed_rmsnorm(residual, delta.delta, delta.gain, delta.eps, delta.mult, self.weight,
+                                                   self.spec.eps, out_dtype or self.ctx.dtype, rows=rows,
+                                                   write_residual=write_residual and rows is None)
         deltas = [d for d in delta if d is not None] if isinstance(delta, (tuple, list)) else ([delta] if delta is not None else [])
         if delta_bias is None and also is None and len(deltas) <= 1:
             return self.ctx.ops.add_rmsnorm(residual, deltas[0] if deltas else None, self.weight, self.spec.eps,

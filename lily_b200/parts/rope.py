@@ -6,7 +6,8 @@ them to the fused norm + rotation + cache-write kernel, which rotates the first 
 features of each head in rotate-half order and passes the rest through.
 
 Frequencies ``base^(-2j/rotary_dim)`` and angles ``position * frequency`` are float32, as in
-lily/layers/rotary.py:49-56; Llama-3 scaling follows rotary.py:99-119.  The tables stay float32
+lily/layers/rotary.py:49-56; Llama-3 scaling follows rotary.py:99-119; "yarn" scaling blends each frequency with
+its slowed value by a ramp over the feature index and stretches both tables (``_yarn``, ``table_stretch``).  The tables stay float32
 in both precisions (the reference casts them to the model dtype, rotary.py:46-47).
 """
 
@@ -49,6 +50,8 @@ def _scaled(inv: torch.Tensor, spec: RopeSpec) -> torch.Tensor:
     s = spec.scaling
     if s.rope_type == "default":
         return inv
+    if s.rope_type == "yarn":
+        return _yarn(inv, spec)
     if s.rope_type != "llama3":
         raise ValueError(f"Unsupported rope scaling type {s.rope_type!r}")
     low_wavelen = s.original_max_position_embeddings / s.low_freq_factor
@@ -61,6 +64,28 @@ def _scaled(inv: torch.Tensor, spec: RopeSpec) -> torch.Tensor:
         smooth = torch.zeros_like(inv)
     mid = (1 - smooth) * inv / s.factor + smooth * inv
     return torch.where(wavelen < high_wavelen, inv, torch.where(wavelen > low_wavelen, inv / s.factor, mid))
+
+
+def _yarn(inv: torch.Tensor, spec: RopeSpec) -> torch.Tensor:
+    """Frequencies blended between their own value and a ``factor``-th of it by a ramp over the feature index: the index
+    at which a wave makes t turns over the original length L is ``dims ln(L / (2 pi t)) / (2 ln theta)``; the ramp
+    rises from 0 at the (floored, at least 0) index of ``fast_turns`` to 1 at the (ceiled, at most dims - 1) index of
+    ``slow_turns``."""
+    s, dims = spec.scaling, spec.rotary_dim
+
+    def index(turns: float) -> float:
+        return dims * math.log(s.original_max_position_embeddings / (2.0 * math.pi * turns)) / (2.0 * math.log(spec.theta))
+    lo = max(math.floor(index(s.fast_turns)), 0)
+    hi = min(math.ceil(index(s.slow_turns)), dims - 1)
+    i = torch.arange(dims // 2, dtype=inv.dtype)
+    ramp = torch.clamp((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    return inv / s.factor * ramp + inv * (1.0 - ramp)
+
+
+def table_stretch(spec: RopeSpec) -> float:
+    """The factor both tables are multiplied by (1 unless the scaling stretches them)."""
+    s = spec.scaling
+    return s.table_stretch_slope * math.log(s.factor) + 1.0 if s.rope_type == "yarn" and s.factor > 0 else 1.0
 
 
 def pairing_order(head_dim: int, rotary_dim: int) -> torch.Tensor:
@@ -84,7 +109,9 @@ class RotaryTable(Part):
                 _TABLES.clear()
             t = torch.arange(ctx.max_position, dtype=torch.float32)
             freqs = torch.outer(t, inverse_frequencies(spec))          # float32 on the host
-            _TABLES[key] = (freqs.cos().contiguous().to(ctx.device), freqs.sin().contiguous().to(ctx.device))
+            stretch = table_stretch(spec)
+            cos, sin = (freqs.cos(), freqs.sin()) if stretch == 1.0 else (freqs.cos() * stretch, freqs.sin() * stretch)
+            _TABLES[key] = (cos.contiguous().to(ctx.device), sin.contiguous().to(ctx.device))
         self._cos, self._sin = _TABLES[key]
 
     def tables(self):

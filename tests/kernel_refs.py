@@ -209,7 +209,8 @@ def uses_tensor_cores(dtype, d):
     return dtype == torch.bfloat16 and d in (64, 128, 192, 256)
 
 
-def prefill_tile_rows(dtype=None, d=0, page_size=0, new_tokens=0, softcap=None, dv=None, values_in_keys=False, heads=0):
+def prefill_tile_rows(dtype=None, d=0, page_size=0, new_tokens=0, softcap=None, dv=None, values_in_keys=False, heads=0,
+                      keep_first=0):
     return 32
 
 
@@ -232,11 +233,12 @@ class DecodePlan:
     stages: int = 0
 
 
-def plan_decode_attention(dtype, requests, nq, nkv, d, max_seq_len, even=False, dv=None, values_in_keys=False):
+def plan_decode_attention(dtype, requests, nq, nkv, d, max_seq_len, even=False, dv=None, values_in_keys=False,
+                          keep_first=0, fusable=True):
     if requests == 0:
         return DecodePlan(1, False, 0, "single")
     splits = 2 if max_seq_len >= 32 else 1
-    fused = FUSE_DECODE and (dv or d) == d
+    fused = FUSE_DECODE and (dv or d) == d and fusable and not keep_first
     return DecodePlan(splits, fused, decode_scratch_floats(requests, nq, dv or d, splits), "wave" if splits > 1 else "single")
 
 
@@ -253,7 +255,7 @@ def _gather_kv(kv_layer, table_row, length, page_size, nkv=None, d=None, dv=None
     return k.float(), v.float()
 
 
-def _attend(q, k, v, q_pos, scale, window, softcap=None):
+def _attend(q, k, v, q_pos, scale, window, softcap=None, keep_first=0):
     """q [rows, nq, d] at positions q_pos [rows]; k [keys, nkv, d], v [keys, nkv, dv] at positions 0..keys-1."""
     rep = q.shape[1] // k.shape[1]
     kk, vv = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)
@@ -263,31 +265,32 @@ def _attend(q, k, v, q_pos, scale, window, softcap=None):
     kpos = torch.arange(k.shape[0], device=q.device)
     seen = kpos[None, :] <= q_pos[:, None]
     if window:
-        seen &= kpos[None, :] > q_pos[:, None] - window
+        seen &= (kpos[None, :] > q_pos[:, None] - window) | (kpos[None, :] < keep_first)
     s = s.masked_fill(~seen[None], float("-inf"))
     return torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), vv)
 
 
 def attention_prefill(q, kv_layer, block_table, cu_seqlens, prefix_lens, tile_req, tile_start, out, nq, nkv, d,
                       page_size, scale, window=None, tile_rows=None, heads_per_block=0, softcap=None, dv=None,
-                      values_in_keys=False):
+                      values_in_keys=False, keep_first=0):
     dv = dv or d
     for r in sorted(set(tile_req.tolist())):
         t0, t1 = int(cu_seqlens[r]), int(cu_seqlens[r + 1])
         prefix = int(prefix_lens[r])
         k, v = _gather_kv(kv_layer, block_table[r], prefix + t1 - t0, page_size, nkv, d, dv, values_in_keys)
         qpos = torch.arange(prefix, prefix + t1 - t0, device=q.device)
-        o = _attend(q[t0:t1].float().view(-1, nq, d), k, v, qpos, scale, window, softcap)
+        o = _attend(q[t0:t1].float().view(-1, nq, d), k, v, qpos, scale, window, softcap, keep_first)
         out[t0:t1] = o.reshape(t1 - t0, nq * dv).to(out.dtype)
 
 
 def attention_decode(q, kv_layer, block_table, seq_lens, out, scratch, splits, nq, nkv, d, page_size, scale,
-                     window=None, stages=0, softcap=None, dv=None, values_in_keys=False):
+                     window=None, stages=0, softcap=None, dv=None, values_in_keys=False, keep_first=0):
     dv = dv or d
     for r in range(q.shape[0]):
         n = int(seq_lens[r])
         k, v = _gather_kv(kv_layer, block_table[r], n, page_size, nkv, d, dv, values_in_keys)
-        o = _attend(q[r:r + 1].float().view(1, nq, d), k, v, torch.tensor([n - 1], device=q.device), scale, window, softcap)
+        o = _attend(q[r:r + 1].float().view(1, nq, d), k, v, torch.tensor([n - 1], device=q.device), scale, window, softcap,
+                    keep_first)
         out[r] = o.reshape(nq * dv).to(out.dtype)
 
 
@@ -331,6 +334,11 @@ def token_chunks(new_lens, chunk, device):
 
 def causal_conv_silu(proj, col0, channels, weight, bias, state, state_off, chunk_req, chunk_start, cu_seqlens, slots,
                      chunk=SSM_CHUNK):
+    return causal_conv(proj, col0, channels, weight, bias, state, state_off, chunk_req, chunk_start, cu_seqlens, slots, chunk)
+
+
+def causal_conv(proj, col0, channels, weight, bias, state, state_off, chunk_req, chunk_start, cu_seqlens, slots,
+                chunk=SSM_CHUNK, activation="silu"):
     taps = weight.shape[1]
     out = torch.empty((proj.shape[0], channels), dtype=proj.dtype, device=proj.device)
     for r in range(cu_seqlens.numel() - 1):
@@ -342,7 +350,7 @@ def causal_conv_silu(proj, col0, channels, weight, bias, state, state_off, chunk
         acc = (bias.float() if bias is not None else torch.zeros(channels))[None, :].expand(t1 - t0, channels).clone()
         for j in range(taps):
             acc = acc + seq[j:j + t1 - t0] * weight[:, j][None, :]
-        out[t0:t1] = (acc * torch.sigmoid(acc)).to(proj.dtype)
+        out[t0:t1] = (acc * torch.sigmoid(acc) if activation == "silu" else acc).to(proj.dtype)
         if taps > 1:
             held.copy_(seq[-(taps - 1):])
     return out
@@ -569,3 +577,76 @@ def moe_experts(h, routing, w_gate_up, w_down, limit, alpha):
             else:
                 out[t] += a * x[t]
     return out
+
+
+# ---------------------------------------------------------------------------- sandwich norms, plain feed-forward
+
+def add_normed_rmsnorm(resid, delta, post_gain, post_eps, mult, weight, eps, out_dtype, rows=None, write_residual=True):
+    """resid += mult * (delta / rms(delta) * post_gain); returns (the new rows) / rms * weight (None without ``weight``)."""
+    d = _sum(delta).float()
+    add = mult * ((d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + post_eps)) * post_gain.float())
+    if rows is not None:
+        v = resid[rows.long()] + add[rows.long()]
+    else:
+        v = resid + add
+        if write_residual:
+            resid.copy_(v)
+    if weight is None:
+        return None
+    return ((v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)) * weight.float()).to(out_dtype)
+
+
+def _activate(z, activation):
+    if activation == "relu2":
+        return torch.clamp(z, min=0) ** 2
+    if activation == "silu":
+        return z * torch.sigmoid(z)
+    assert activation == "gelu_tanh"
+    return 0.5 * z * (1 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z ** 3)))
+
+
+def activation(x, out_dtype, activation="relu2"):
+    return _activate(_sum(x).float(), activation).to(out_dtype)
+
+
+def linear_activation(x, weight, activation="relu2"):
+    return _activate(_sum(linear_auto(x, weight)).float(), activation).to(x.dtype)
+
+
+# ---------------------------------------------------------------------------- differential attention
+
+def diff_prepare(proj, positions, token_req, block_table, kv_layer, heads, nkv, d, dv, maps, page_size, temp_coef, temp_every,
+                 write_kv=True):
+    """proj [tokens, heads*maps*d | nkv*maps*d | nkv*dv | ...]: queries times 1 + coef ln(floor((p + 1) / every) + 1), map m of
+    head h laid out as query head h*maps + m of maps*d columns, zero outside columns [m*d, (m+1)*d); keys and values to the page."""
+    n = proj.shape[0]
+    x = proj.float()
+    kd = maps * d
+    q = x[:, :heads * kd].view(n, heads, maps, d)
+    if temp_coef:
+        p = positions.float()
+        q = q * (1.0 + temp_coef * torch.log(torch.floor((p + 1.0) / float(temp_every)) + 1.0))[:, None, None, None]
+    wide = torch.zeros((n, heads, maps, maps, d), dtype=torch.float32, device=proj.device)
+    for m in range(maps):
+        wide[:, :, m, m] = q[:, :, m]
+    if write_kv:
+        k = x[:, heads * kd:(heads + nkv) * kd].view(n, nkv, kd)
+        v = x[:, (heads + nkv) * kd:(heads + nkv) * kd + nkv * dv].view(n, nkv, dv)
+        pos = positions.long()
+        page = block_table[token_req.long(), pos // page_size].long()
+        keys, values = _pages(kv_layer, nkv, page_size, kd, dv)
+        keys[page, :, pos % page_size] = k.to(kv_layer.dtype)
+        values[page, :, pos % page_size] = v.to(kv_layer.dtype)
+    return wide.reshape(n, heads * maps * kd).to(kv_layer.dtype)
+
+
+def diff_combine(maps_out, proj, gate_col, heads, dv, maps, lam, out_scale, eps):
+    """maps_out [tokens, heads*maps*dv]; o = a_0 - lam * a_1, divided by its root mean square over dv, times out_scale,
+    times sigmoid(proj[:, gate_col + head])."""
+    assert maps == 2
+    n = maps_out.shape[0]
+    a = maps_out.float().view(n, heads, maps, dv)
+    o = a[:, :, 0] - lam * a[:, :, 1]
+    o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * out_scale
+    gate = torch.sigmoid(proj[:, gate_col:gate_col + heads].float())
+    return (o * gate[:, :, None]).reshape(n, heads * dv).to(maps_out.dtype)

@@ -16,7 +16,8 @@
 //    partial (max, sum, output) go to scratch and are merged by the combine kernel.
 //
 // Scores q.k * scale (soft-capped to softcap * tanh(. / softcap) when a cap is given), keys visible when key position <= query position (and > query position -
-// window when a window is given), softmax and p.v in float32: the formulas of
+// window when a window is given, or below `keep_first`: a window that keeps a request's first positions in sight.  A
+// block then walks two runs of keys as one: the kept positions that lie before its window, then the window's), softmax and p.v in float32: the formulas of
 // lily/layers/attention/torch_native_backend.py:31-37,52-77; the split over keys follows
 // lily/layers/attention/triton_ops/decode_attention.py:21-157, the prefix + new tokens form
 // lily/layers/attention/triton_ops/extend_attention.py:17-169.
@@ -48,7 +49,9 @@ attention_simt_kernel(const AttnArgs a) {
     T* out = (T*)a.out;
     const int group = a.nq / a.nkv;
 
-    int req, kvh, kbeg, kend, nrows;
+    // the block's keys are numbered u = ubeg .. uend - 1 over two runs: the first `nkeep` are positions 0 .. nkeep - 1
+    // (kept first positions behind the window), the rest positions klo, klo + 1, ...
+    int req, kvh, ubeg, uend, nkeep, klo, nrows;
     int row_tok[RPW], row_head[RPW], row_pos[RPW];
     bool row_ok[RPW];
     if (DECODE) {
@@ -57,11 +60,13 @@ attention_simt_kernel(const AttnArgs a) {
         kvh = blockIdx.y / chunks;
         const int r0 = (blockIdx.y % chunks) * ROWS;
         const int seq = a.seq_lens[req];
-        const int lo = (a.window > 0 && seq > a.window) ? seq - a.window : 0;
-        int per = (seq - lo + a.splits - 1) / a.splits;
+        klo = (a.window > 0 && seq > a.window) ? seq - a.window : 0;
+        nkeep = min(a.keep_first, klo);
+        const int total = nkeep + seq - klo;
+        int per = (total + a.splits - 1) / a.splits;
         per = (per + KEYS - 1) / KEYS * KEYS;
-        kbeg = lo + blockIdx.z * per;
-        kend = min(seq, kbeg + per);
+        ubeg = blockIdx.z * per;
+        uend = min(total, ubeg + per);
         nrows = min(ROWS, group - r0);
 #pragma unroll
         for (int i = 0; i < RPW; ++i) {
@@ -80,8 +85,10 @@ attention_simt_kernel(const AttnArgs a) {
         const int head = blockIdx.y;
         kvh = head / group;
         nrows = min(ROWS, len - start);
-        kend = prefix + start + nrows;
-        kbeg = (a.window > 0 && prefix + start + 1 > a.window) ? prefix + start + 1 - a.window : 0;
+        klo = (a.window > 0 && prefix + start + 1 > a.window) ? prefix + start + 1 - a.window : 0;
+        nkeep = min(a.keep_first, klo);
+        ubeg = 0;
+        uend = nkeep + prefix + start + nrows - klo;
 #pragma unroll
         for (int i = 0; i < RPW; ++i) {
             const int r = warp * RPW + i;
@@ -114,12 +121,13 @@ attention_simt_kernel(const AttnArgs a) {
     const size_t page_stride = (size_t)a.nkv * (khead + vhead);
     const float cap = a.softcap, cap_in = cap > 0.f ? a.scale / cap : 0.f;
 
-    for (int kb = kbeg; kb < kend; kb += KEYS) {
+    for (int ub = ubeg; ub < uend; ub += KEYS) {
         __syncthreads();
         // load the key and value tiles: KEYS rows of d, a warp per row at a time
         for (int j = warp; j < KEYS; j += WARPS) {
-            const int kpos = kb + j;
-            if (kpos < kend) {
+            const int u = ub + j;
+            const int kpos = u < nkeep ? u : klo + (u - nkeep);
+            if (u < uend) {
                 const int page = table[kpos / a.page_size];
                 const T* base = kv + (size_t)page * page_stride;
                 const T* ksrc = base + (size_t)kvh * khead + (size_t)(kpos % a.page_size) * d;
@@ -148,11 +156,12 @@ attention_simt_kernel(const AttnArgs a) {
                 s[i] = fmaf(Qs[r * d + c], kval, s[i]);
             }
         }
-        const int kpos = kb + lane;
+        const int u = ub + lane;
+        const int kpos = u < nkeep ? u : klo + (u - nkeep);
 #pragma unroll
         for (int i = 0; i < RPW; ++i) {
-            const bool seen = row_ok[i] && kpos < kend && kpos <= row_pos[i] &&
-                              (a.window <= 0 || kpos > row_pos[i] - a.window);
+            const bool seen = row_ok[i] && u < uend && kpos <= row_pos[i] &&
+                              (a.window <= 0 || kpos > row_pos[i] - a.window || kpos < a.keep_first);
             const float sv = seen ? (cap > 0.f ? cap * tanhf(s[i] * cap_in) : s[i] * a.scale) : -INFINITY;
             const float m_new = fmaxf(m[i], warp_max(sv));
             float p = 0.f, alpha = 1.f;
@@ -341,7 +350,7 @@ LILY_API int lily_attention_prefill_simt(const void* q, const void* kv, void* ou
                                          int bt_stride, const int* cu_seqlens, const int* prefix_lens,
                                          const int* tile_req, const int* tile_start, int tiles, int nq, int nkv,
                                          int d, int page_size, int window, float scale, int dtype,
-                                         float softcap, int dv, cudaStream_t stream) {
+                                         float softcap, int dv, int keep_first, cudaStream_t stream) {
     if (tiles == 0) return 0;
     if (check_common("attention_prefill", nq, nkv, d, page_size, dv)) return 1;
     LILY_REQUIRE(nq <= 65535, "attention_prefill: %d query heads", nq);
@@ -350,6 +359,7 @@ LILY_API int lily_attention_prefill_simt(const void* q, const void* kv, void* ou
     a.cu_seqlens = cu_seqlens; a.prefix_lens = prefix_lens; a.tile_req = tile_req; a.tile_start = tile_start;
     a.splits = 1; a.nq = nq; a.nkv = nkv; a.d = d; a.page_size = page_size; a.window = window; a.scale = scale;
     a.softcap = softcap; a.dv = dv > 0 ? dv : (dv < 0 ? -dv : d); a.v_in_k = dv < 0;
+    a.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
     dim3 grid(tiles, nq);
     int rc = dtype == kBF16 ? launch<__nv_bfloat16, false>(a, grid, stream) : launch<float, false>(a, grid, stream);
     if (rc) return rc;
@@ -383,7 +393,8 @@ LILY_API size_t lily_attention_decode_scratch_floats(int requests, int nq, int d
 LILY_API int lily_attention_decode_simt(const void* q, const void* kv, void* out, const int* block_table,
                                         int bt_stride, const int* seq_lens, float* scratch, int requests,
                                         int splits, int nq, int nkv, int d, int page_size, int window,
-                                        float scale, int dtype, float softcap, int dv, cudaStream_t stream) {
+                                        float scale, int dtype, float softcap, int dv, int keep_first,
+                                        cudaStream_t stream) {
     if (requests == 0) return 0;
     if (check_common("attention_decode", nq, nkv, d, page_size, dv)) return 1;
     const int d_out = dv > 0 ? dv : (dv < 0 ? -dv : d);
@@ -394,6 +405,7 @@ LILY_API int lily_attention_decode_simt(const void* q, const void* kv, void* out
     a.q = q; a.kv = kv; a.out = out; a.block_table = block_table; a.bt_stride = bt_stride;
     a.seq_lens = seq_lens; a.splits = splits; a.nq = nq; a.nkv = nkv; a.d = d; a.page_size = page_size;
     a.window = window; a.scale = scale; a.softcap = softcap; a.dv = d_out; a.v_in_k = dv < 0;
+    a.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
     a.part_o = scratch;
     a.part_ml = scratch ? scratch + (size_t)requests * nq * splits * d_out : nullptr;
     dim3 grid(requests, nkv * chunks, splits);

@@ -35,8 +35,8 @@ _SIGNATURES = {
     "lily_skinny_swiglu": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "lily_cast": [_vp, _i, _vp, _i, _sz, _vp],
     "lily_gemm_fp32": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
-    "lily_attention_prefill_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _vp],
-    "lily_attention_decode_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _vp],
+    "lily_attention_prefill_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _i, _vp],
+    "lily_attention_decode_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _i, _vp],
     "lily_attention_combine": [_vp, _vp, _i, _i, _i, _i, _i, _vp],
     "lily_attention_prefill_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _vp],
     "lily_attention_prefill_tc": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _f, _vp],
@@ -46,6 +46,11 @@ _SIGNATURES = {
     "lily_sigmoid_gate": [_vp, _i, _vp, _i, _i, _sz, _sz, _vp],
     "lily_normed_mean": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _sz, _vp, _i, _i, _f, _f, _vp],
     "lily_causal_conv_silu": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _sz, _sz, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _vp],
+    "lily_causal_conv": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _sz, _sz, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _vp],
+    "lily_add_normed_rmsnorm": [_vp, _vp, _i, _i, _sz, _vp, _f, _f, _vp, _i, _vp, _i, _vp, _i, _i, _f, _i, _vp],
+    "lily_activation": [_vp, _i, _i, _sz, _vp, _i, _sz, _i, _vp],
+    "lily_diff_prepare": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp],
+    "lily_diff_combine": [_vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _f, _f, _i, _vp],
     "lily_ssd_scan": [_vp, _i, _vp, _i, _i, _vp, _vp, _vp, _vp, _sz, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp,
                       _i, _vp, _vp, _i, _vp],
     "lily_ssd_combine": [_vp, _sz, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
@@ -558,13 +563,13 @@ def latent_attention_status() -> int:
 
 def prefill_tile_rows(dtype: torch.dtype = torch.float32, d: int = 0, page_size: int = 0, new_tokens: int = 0,
                       softcap: Optional[float] = None, dv: Optional[int] = None, values_in_keys: bool = False,
-                      heads: int = 0) -> int:
+                      heads: int = 0, keep_first: int = 0) -> int:
     """New tokens per tile of the prefill kernel that will take this precision, head size (``dv`` for the values
-    where it differs), page size, number of new tokens and kind of scores."""
+    where it differs), page size, number of new tokens and kind of scores and mask."""
     lib = library()
     if values_in_keys and heads and latent_tensor_cores(dtype, d, dv, softcap=softcap):
         return int(lib.lily_latent_attention_mma_tile_tokens(int(heads)))
-    same = (dv is None or dv == d) and not values_in_keys
+    same = (dv is None or dv == d) and not values_in_keys and not keep_first
     if same and uses_tcgen05_attention(dtype, d, page_size, new_tokens):
         return int(lib.lily_attention_prefill_tc_rows())
     return int(lib.lily_attention_prefill_mma_rows() if same and uses_tensor_cores(dtype, d) else lib.lily_attention_prefill_simt_rows())
@@ -579,9 +584,10 @@ def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torc
                       prefix_lens: torch.Tensor, tile_req: torch.Tensor, tile_start: torch.Tensor, out: torch.Tensor,
                       nq: int, nkv: int, d: int, page_size: int, scale: float, window: Optional[int] = None,
                       tile_rows: Optional[int] = None, heads_per_block: int = 0, softcap: Optional[float] = None,
-                      dv: Optional[int] = None, values_in_keys: bool = False) -> None:
+                      dv: Optional[int] = None, values_in_keys: bool = False, keep_first: int = 0) -> None:
     """Causal attention of each request's new tokens over its cached prefix and themselves.  ``softcap``: scores
-    become softcap * tanh(score * scale / softcap) before the softmax; ``dv``: the
+    become softcap * tanh(score * scale / softcap) before the softmax; ``keep_first``: beside a window, keys at
+    positions below this stay visible (CUDA-core kernels); ``dv``: the
     value head size where it differs from d (CUDA-core kernels; ``out`` is then [tokens, nq * dv]).
     ``values_in_keys``: the values are the first ``dv`` columns of the key rows and a page holds keys only (CUDA-core kernels).
     ``q`` and ``out`` are [tokens, nq * d] indexed by ``cu_seqlens``; tiles list (request, offset)
@@ -604,11 +610,12 @@ def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torc
               _i32(tile_req, "tile_req"), _i32(tile_start, "tile_start"), tile_req.numel(), int(tile_rows), nq, d, dv,
               page_size, int(window or 0), float(scale), _stream())
         return
-    tensor_cores = dv == d and not values_in_keys and uses_tensor_cores(q.dtype, d)
+    keep_first = int(keep_first or 0) if window else 0
+    tensor_cores = dv == d and not values_in_keys and not keep_first and uses_tensor_cores(q.dtype, d)
     base_rows = int(lib.lily_attention_prefill_mma_rows() if tensor_cores else lib.lily_attention_prefill_simt_rows())
     if tile_rows is not None and tile_rows != base_rows:
         if not (tile_rows == int(lib.lily_attention_prefill_tc_rows()) and q.dtype == torch.bfloat16 and dv == d
-                and lib.lily_attention_prefill_tc_takes(int(d), int(page_size))):
+                and not keep_first and lib.lily_attention_prefill_tc_takes(int(d), int(page_size))):
             raise KernelError(f"attention_prefill: no kernel with tiles of {tile_rows} rows for {q.dtype}, head size {d}, "
                               f"page size {page_size}")
         if not (q.is_contiguous() and out.is_contiguous() and kv_layer.is_contiguous()):
@@ -617,7 +624,7 @@ def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torc
     elif tensor_cores:
         _call("lily_attention_prefill_mma", *common, cap, _stream())
     else:
-        _call("lily_attention_prefill_simt", *common, _dt(q), cap, -dv if values_in_keys else dv, _stream())
+        _call("lily_attention_prefill_simt", *common, _dt(q), cap, -dv if values_in_keys else dv, keep_first, _stream())
 
 
 def decode_clusters(d: int, splits: int, group: int) -> int:
@@ -633,9 +640,10 @@ def decode_scratch_floats(requests: int, nq: int, d: int, splits: int) -> int:
 def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor,
                      out: torch.Tensor, scratch: Optional[torch.Tensor], splits: int, nq: int, nkv: int, d: int,
                      page_size: int, scale: float, window: Optional[int] = None, stages: int = 0,
-                     softcap: Optional[float] = None, dv: Optional[int] = None, values_in_keys: bool = False) -> None:
+                     softcap: Optional[float] = None, dv: Optional[int] = None, values_in_keys: bool = False,
+                     keep_first: int = 0) -> None:
     """One query token per request (rows of ``q`` [requests, nq * d]) over ``seq_lens`` cached
-    positions, keys cut into ``splits`` ranges merged through ``scratch`` (float32).  ``stages`` (tensor-core
+    positions (the last ``window`` of them and the first ``keep_first``, where given), keys cut into ``splits`` ranges merged through ``scratch`` (float32).  ``stages`` (tensor-core
     kernel only): the key/value tiles a block holds, 0 for the default (``DecodePlan.stages``)."""
     _dev(q, kv_layer, block_table, seq_lens, out, scratch)
     requests = q.shape[0]
@@ -655,14 +663,15 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
               int(window or 0), float(scale), _stream())
         if splits > 1:
             _call("lily_attention_combine", _p(scratch), _p(out), requests, nq, dv, splits, _dt(q), _stream())
-    elif dv == d and not values_in_keys and uses_tensor_cores(q.dtype, d):
+    elif dv == d and not values_in_keys and not (keep_first and window) and uses_tensor_cores(q.dtype, d):
         _call("lily_attention_decode_mma", *common, int(stages), cap, _stream())   # merges the splits itself (cluster, or combine behind)
         if splits > 1 and (stages or requests * nkv * -(-(nq // nkv) // 16) > decode_clusters(d, splits, nq // nkv)):
             launches["count"] += 1                                   # the combine kernel, launched inside
     else:
         if stages:
             raise KernelError(f"attention_decode: {stages} stages are the tensor-core kernel's; {q.dtype}, head size {d} runs on CUDA cores")
-        _call("lily_attention_decode_simt", *common, _dt(q), cap, -dv if values_in_keys else dv, _stream())
+        _call("lily_attention_decode_simt", *common, _dt(q), cap, -dv if values_in_keys else dv,
+              int(keep_first or 0) if window else 0, _stream())
         if splits > 1:
             launches["count"] += 1          # the combine kernel, launched inside
 
@@ -742,12 +751,15 @@ def whole_rows_pay(pairs: int, sm_count: int = 148) -> bool:
 
 
 def plan_decode_attention(dtype: torch.dtype, requests: int, nq: int, nkv: int, d: int, max_seq_len: int,
-                          even: bool = False, dv: Optional[int] = None, values_in_keys: bool = False) -> DecodePlan:
+                          even: bool = False, dv: Optional[int] = None, values_in_keys: bool = False,
+                          keep_first: int = 0, fusable: bool = True) -> DecodePlan:
     """The plan for ``requests`` rows that bring one token each, none longer than ``max_seq_len`` positions.
     A step in which every request brings one token may hand the qkv product straight to the attention kernel
     (``fused``): every block then finishes its own queries, which costs less than a kernel of its own while all
     blocks are resident at once (three a SM) and more when they run in several rounds (measured at batch 64:
     2 % of the step).
+    ``fusable`` False: the caller prepares queries and cache itself (something stands between its projection and
+    the attention); ``keep_first``: the window keeps the first positions in sight (CUDA-core kernel).
     ``even``: the caller knows that the rows are about equally long (the longest at most an eighth over their
     mean).  Then, and when ``whole_rows_pay``, a block
     takes all keys of its row with three stages; rows of very different lengths keep their ranges, which spread a
@@ -756,15 +768,15 @@ def plan_decode_attention(dtype: torch.dtype, requests: int, nq: int, nkv: int, 
         return DecodePlan(1, False, 0, "single")
     group = nq // nkv
     dv = int(dv or d)
-    tensor_cores = dv == d and not values_in_keys and uses_tensor_cores(dtype, d)      # values of another head size run on CUDA cores
+    tensor_cores = dv == d and not values_in_keys and not keep_first and uses_tensor_cores(dtype, d)      # values of another head size run on CUDA cores
     row_blocks = -(-group // 16)                 # the tensor-core kernel takes 16 query heads of a kv head a block
     pairs = requests * nkv * row_blocks
     if even and tensor_cores and d <= 128 and _WHOLE_ROWS and whole_rows_pay(pairs, sm_count()):
-        return DecodePlan(1, pairs <= 2 * sm_count(), 0, "whole rows", 3)
+        return DecodePlan(1, fusable and pairs <= 2 * sm_count(), 0, "whole rows", 3)
     room = (lambda s: decode_clusters(d, s, group)) if tensor_cores else None
     splits = choose_decode_splits(requests, nkv, max_seq_len, sm_count=sm_count(), clusters=room)
     in_clusters = tensor_cores and splits > 1 and pairs <= decode_clusters(d, splits, group)
-    fused = tensor_cores and pairs * splits <= 3 * sm_count()
+    fused = fusable and tensor_cores and pairs * splits <= 3 * sm_count()
     arm = "single" if splits == 1 else ("cluster" if in_clusters else "wave")
     return DecodePlan(splits, fused, decode_scratch_floats(requests, nq, dv, splits), arm)
 
@@ -897,6 +909,29 @@ def causal_conv_silu(proj: torch.Tensor, col0: int, channels: int, weight: torch
     _call("lily_causal_conv_silu", _p(proj), width, int(col0), int(channels), int(taps), _p(weight), _p(bias), _p(state),
           state.shape[1], int(state_off), _p(out), _i32(chunk_req, "chunk_req"), _i32(chunk_start, "chunk_start"),
           chunk_req.numel(), int(chunk), _i32(cu_seqlens, "cu_seqlens"), _i32(slots, "slots"), _dt(proj), _stream())
+    return out
+
+
+def causal_conv(proj: torch.Tensor, col0: int, channels: int, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                state: torch.Tensor, state_off: int, chunk_req: torch.Tensor, chunk_start: torch.Tensor,
+                cu_seqlens: torch.Tensor, slots: torch.Tensor, chunk: int = SSM_CHUNK, activation: str = "silu") -> torch.Tensor:
+    """``causal_conv_silu`` with the activation named: "silu", or "none" for the convolution alone."""
+    if activation not in ("silu", "none"):
+        raise KernelError(f"causal_conv: no activation {activation!r}; have 'silu' and 'none'")
+    _dev(proj, weight, bias, state, chunk_req, chunk_start, cu_seqlens, slots)
+    n, width = proj.shape
+    taps = weight.shape[1]
+    if weight.dtype != torch.float32 or tuple(weight.shape) != (channels, taps) or state.dtype != torch.float32:
+        raise KernelError("causal_conv: float32 weights [channels, taps] and a float32 state")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != channels):
+        raise KernelError("causal_conv: the bias is float32 [channels]")
+    if state.dim() != 2 or state_off + (taps - 1) * channels > state.shape[1] or col0 + channels > width:
+        raise KernelError("causal_conv: columns or state out of range")
+    out = torch.empty((n, channels), dtype=proj.dtype, device=proj.device)
+    _call("lily_causal_conv", _p(proj), width, int(col0), int(channels), int(taps), _p(weight), _p(bias), _p(state),
+          state.shape[1], int(state_off), _p(out), _i32(chunk_req, "chunk_req"), _i32(chunk_start, "chunk_start"),
+          chunk_req.numel(), int(chunk), _i32(cu_seqlens, "cu_seqlens"), _i32(slots, "slots"), _dt(proj),
+          1 if activation == "silu" else 0, _stream())
     return out
 
 
@@ -1391,3 +1426,92 @@ def top_logprobs(logits: torch.Tensor, k: torch.Tensor):
     counts = torch.empty((rows,), dtype=torch.int32, device=logits.device)
     _call("lily_top_logprobs", _p(logits), _i32(k, "k"), _p(tokens), _p(logprobs), _p(counts), rows, vocab, _stream())
     return tokens, logprobs, counts
+
+
+# ------------------------------------------------------------------------------ norms on both sides of a sublayer, plain feed-forward
+
+PLAIN_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu2": 2}
+
+
+def add_normed_rmsnorm(resid: torch.Tensor, delta: torch.Tensor, post_gain: torch.Tensor, post_eps: float, mult: float,
+                       weight: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
+                       rows: Optional[torch.Tensor] = None, write_residual: bool = True) -> Optional[torch.Tensor]:
+    """``resid += mult * (delta / rms(delta) * post_gain)`` in float32 (``delta`` [tokens, width] in either dtype, or
+    float32 partial sums [splits, tokens, width]), then the new rows divided by their root mean square times ``weight``
+    in ``out_dtype`` (None without ``weight``: the add alone).  With ``rows`` only those tokens' outputs are formed and
+    the stream is left as it is."""
+    _dev(resid, delta, post_gain, weight, rows)
+    n, width = resid.shape
+    if resid.dtype != torch.float32 or post_gain.dtype != torch.float32 or post_gain.numel() != width:
+        raise KernelError("add_normed_rmsnorm: the residual stream and the gain behind the sublayer are float32")
+    ptr, dt, splits, stride = _operand(delta, n, width, "add_normed_rmsnorm delta")
+    if rows is not None and write_residual:
+        raise KernelError("add_normed_rmsnorm: gathered rows are not written back")
+    n_out = n if rows is None else rows.numel()
+    out = None
+    if weight is not None:
+        if weight.numel() != width:
+            raise KernelError("add_normed_rmsnorm: gain of another width")
+        out = torch.empty((n_out, width), dtype=out_dtype, device=resid.device)
+    elif rows is not None:
+        return None
+    _call("lily_add_normed_rmsnorm", _p(resid), ptr, dt, splits, stride, _p(post_gain), float(post_eps), float(mult),
+          _p(weight), _dt(weight) if weight is not None else _F32, _p(out), _dt(out) if out is not None else _F32,
+          _i32(rows, "rows"), n_out, width, float(eps), int(bool(write_residual)), _stream())
+    return out
+
+
+def activation(x: torch.Tensor, out_dtype: torch.dtype, activation: str = "relu2") -> torch.Tensor:
+    """``act(x)`` elementwise: "relu2" (the square of max(., 0)), "silu" or "gelu_tanh"; ``x`` [tokens, cols] in either
+    dtype or float32 partial sums [splits, tokens, cols]."""
+    if activation not in PLAIN_ACTIVATIONS:
+        raise KernelError(f"no activation {activation!r}; have {sorted(PLAIN_ACTIVATIONS)}")
+    _dev(x)
+    n, cols = x.shape[-2:]
+    ptr, dt, splits, stride = _operand(x, n, cols, "activation")
+    out = torch.empty((n, cols), dtype=out_dtype, device=x.device)
+    _call("lily_activation", ptr, dt, splits, stride, _p(out), _dt(out), out.numel(), PLAIN_ACTIVATIONS[activation], _stream())
+    return out
+
+
+def linear_activation(x: torch.Tensor, weight: torch.Tensor, activation_name: str = "relu2") -> torch.Tensor:
+    """``act(x @ weight.T)`` in ``x``'s dtype: the product (whole, or float32 partial sums for a few tokens) with the
+    activation as a pass over it."""
+    return activation(linear_auto(x, weight), x.dtype, activation_name)
+
+
+# ------------------------------------------------------------------------------ differential attention
+
+def diff_prepare(proj: torch.Tensor, positions: torch.Tensor, token_req: torch.Tensor, block_table: torch.Tensor,
+                 kv_layer: torch.Tensor, heads: int, nkv: int, d: int, dv: int, maps: int, page_size: int,
+                 temp_coef: float, temp_every: int, write_kv: bool = True) -> torch.Tensor:
+    """``proj`` [tokens, heads*maps*d | nkv*maps*d | nkv*dv | ...] in the cache's dtype.  Returns the queries
+    [tokens, heads*maps * maps*d]: map m of head h as query head h*maps + m whose columns [m d, (m+1) d) hold the map's
+    query times ``1 + temp_coef ln(floor((p + 1) / temp_every) + 1)`` and whose other columns are zero; writes each
+    token's keys (rows of maps*d) and values to its place in its page (``cache_layer_fits`` with d = maps*d)."""
+    _dev(proj, positions, token_req, block_table, kv_layer)
+    n, width = proj.shape
+    kd = maps * d
+    if proj.dtype != kv_layer.dtype:
+        raise KernelError(f"cache dtype {kv_layer.dtype} differs from activations {proj.dtype}")
+    cache_layer_fits(kv_layer, nkv, page_size, kd, dv)
+    q = torch.empty((n, heads * maps * kd), dtype=proj.dtype, device=proj.device)
+    _call("lily_diff_prepare", _p(proj), width, _i32(positions, "positions"), _i32(token_req, "token_req"),
+          _i32(block_table, "block_table"), block_table.shape[-1], _p(kv_layer), _p(q), n, heads, nkv, d, dv, maps,
+          page_size, float(temp_coef), int(temp_every), int(write_kv), _dt(proj), _stream())
+    return q
+
+
+def diff_combine(maps_out: torch.Tensor, proj: torch.Tensor, gate_col: int, heads: int, dv: int, maps: int, lam: float,
+                 out_scale: float, eps: float) -> torch.Tensor:
+    """``maps_out`` [tokens, heads*maps*dv] (the maps' attention outputs, head by head): per head
+    ``o = a_0 - lam a_1``, divided by its root mean square over dv, times ``out_scale``, times
+    ``sigmoid(proj[:, gate_col + head])``; returns [tokens, heads*dv]."""
+    _dev(maps_out, proj)
+    n = maps_out.shape[0]
+    if maps_out.dtype != proj.dtype or maps_out.shape[1] != heads * maps * dv:
+        raise KernelError("diff_combine: the maps' outputs are [tokens, heads*maps*dv] in the projection's dtype")
+    out = torch.empty((n, heads * dv), dtype=maps_out.dtype, device=maps_out.device)
+    _call("lily_diff_combine", _p(maps_out), _p(proj), proj.shape[1], int(gate_col), _p(out), n, heads, dv, maps,
+          float(lam), float(out_scale), float(eps), _dt(maps_out), _stream())
+    return out

@@ -33,7 +33,8 @@ __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log
 // consecutive new tokens of one request (chunks start at multiples of chunk_len >= taps - 1 from the portion's
 // first token, so only a portion's first chunk reads the carried inputs; the thread of that chunk also writes
 // them back, after it has read them, so no other thread touches what it reads).
-template <typename T, int TAPS>
+// SILU false: the convolution alone (a mixer that convolves its projections and applies no activation).
+template <typename T, int TAPS, bool SILU = true>
 __global__ void causal_conv_silu_kernel(const T* __restrict__ in, int in_stride, int col0, int channels,
                                         const float* __restrict__ w, const float* __restrict__ bias,
                                         float* __restrict__ state, size_t state_stride, size_t state_off,
@@ -83,7 +84,7 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ in, int in_stride,
 #pragma unroll
                 for (int j = 0; j + 1 < K1; ++j) win[j] = win[j + 1];
                 if (K1 > 0) win[K1 - 1] = x;
-                dst[(size_t)u * channels] = from_float<T>(silu_for<T>(acc));
+                dst[(size_t)u * channels] = from_float<T>(SILU ? silu_for<T>(acc) : acc);
             }
         }
         from += (size_t)4 * in_stride;
@@ -429,19 +430,24 @@ using namespace lily;
 
 LILY_API int lily_conv_max_taps() { return 8; }
 
-LILY_API int lily_causal_conv_silu(const void* in, int in_stride, int col0, int channels, int taps, const float* w,
-                                   const float* bias, float* state, size_t state_stride, size_t state_off, void* out,
-                                   const int* chunk_req, const int* chunk_start, int chunks, int chunk_len,
-                                   const int* cu_seqlens, const int* slots, int dtype, cudaStream_t stream) {
+// act: 1 SiLU, 0 none
+LILY_API int lily_causal_conv(const void* in, int in_stride, int col0, int channels, int taps, const float* w,
+                              const float* bias, float* state, size_t state_stride, size_t state_off, void* out,
+                              const int* chunk_req, const int* chunk_start, int chunks, int chunk_len,
+                              const int* cu_seqlens, const int* slots, int dtype, int act, cudaStream_t stream) {
     if (chunks == 0 || channels == 0) return 0;
+    LILY_REQUIRE(act == 0 || act == 1, "causal_conv: activation %d (0 none, 1 SiLU)", act);
     LILY_REQUIRE(taps >= 1 && taps <= 8, "causal_conv_silu: %d taps (1 to 8)", taps);
     LILY_REQUIRE(chunk_len >= taps - 1 && chunk_len >= 1, "causal_conv_silu: chunks of %d tokens for %d taps", chunk_len, taps);
     LILY_REQUIRE(chunks <= 65535, "causal_conv_silu: %d chunks", chunks);
     dim3 grid((channels + 127) / 128, chunks), block(128);
-#define GO(T, K)                                                                                                     \
-    launch_pdl(causal_conv_silu_kernel<T, K>, grid, block, 0, stream, (const T*)in, in_stride, col0, channels, w, bias, \
+#define GO(T, K, A)                                                                                                  \
+    launch_pdl(causal_conv_silu_kernel<T, K, A>, grid, block, 0, stream, (const T*)in, in_stride, col0, channels, w, bias, \
                state, state_stride, state_off, (T*)out, chunk_req, chunk_start, chunk_len, cu_seqlens, slots)
-#define TAPS_CASE(K) case K: if (dtype == kBF16) GO(__nv_bfloat16, K); else GO(float, K); break;
+#define TAPS_CASE(K) case K:                                                                \
+        if (dtype == kBF16) { if (act) GO(__nv_bfloat16, K, true); else GO(__nv_bfloat16, K, false); } \
+        else { if (act) GO(float, K, true); else GO(float, K, false); }                     \
+        break;
     switch (taps) {
         TAPS_CASE(1) TAPS_CASE(2) TAPS_CASE(3) TAPS_CASE(4) TAPS_CASE(5) TAPS_CASE(6) TAPS_CASE(7) TAPS_CASE(8)
     }
@@ -449,6 +455,14 @@ LILY_API int lily_causal_conv_silu(const void* in, int in_stride, int col0, int 
 #undef GO
     LILY_CHECK_LAUNCH("causal_conv_silu");
     return 0;
+}
+
+LILY_API int lily_causal_conv_silu(const void* in, int in_stride, int col0, int channels, int taps, const float* w,
+                                   const float* bias, float* state, size_t state_stride, size_t state_off, void* out,
+                                   const int* chunk_req, const int* chunk_start, int chunks, int chunk_len,
+                                   const int* cu_seqlens, const int* slots, int dtype, cudaStream_t stream) {
+    return lily_causal_conv(in, in_stride, col0, channels, taps, w, bias, state, state_stride, state_off, out, chunk_req,
+                            chunk_start, chunks, chunk_len, cu_seqlens, slots, dtype, 1, stream);
 }
 
 LILY_API int lily_ssd_scan_max_state() { return 512; }

@@ -37,7 +37,7 @@ struct AttnArgs {
     int dv;                   // value head size where it differs from d (CUDA-core kernels; 0: d); a page then holds its
                               // keys [kv_heads, page_size, d] followed by its values [kv_heads, page_size, dv]
     int v_in_k;               // CUDA-core kernels: the values are the first dv columns of the key rows; a page holds keys only
-    int keep_first;           // with a window: keys at positions below this stay visible whatever the distance (CUDA-core kernels)
+    int keep_first;           // with a window: keys at positions below this stay visible whatever the distance
     int stages;               // decode, tensor-core kernel: key/value tiles a block keeps in shared memory (0: the default, 2;
                               // 3: two blocks a SM instead of three, each with two tiles in flight; head sizes up to 128)
 };

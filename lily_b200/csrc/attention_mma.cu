@@ -176,19 +176,26 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
     const int* table = a.block_table + (size_t)req * a.bt_stride;
     const size_t head_stride = (size_t)a.page_size * D;
     const size_t page_stride = 2 * (size_t)a.nkv * head_stride;
-    const int ntiles = kend > kbeg ? (kend - kbeg + BN - 1) / BN : 0;
+    // With a window that keeps the first positions in sight, the keys [0, kept) that lie before the range come first, in
+    // tiles of their own (the block of the first range only, where the ranges of a row are cut): tile t covers the keys
+    // from tile_base(t) up to tile_limit(t).
+    const int kept = (a.window > 0 && a.keep_first > 0 && (!DECODE || blockIdx.z == 0)) ? min(a.keep_first, kbeg) : 0;
+    const int ftiles = (kept + BN - 1) / BN;
+    const int ntiles = ftiles + (kend > kbeg ? (kend - kbeg + BN - 1) / BN : 0);
+    auto tile_base = [&](int t) { return t < ftiles ? t * BN : kbeg + (t - ftiles) * BN; };
+    auto tile_limit = [&](int t) { return t < ftiles ? kept : kend; };
 
     const __nv_bfloat16* kv_head = kv + (size_t)kvh * head_stride;
     const int page_mask = (1 << page_shift) - 1;
     auto load_tile = [&](int t, int buf) {
-        const int kb = kbeg + t * BN;
+        const int kb = tile_base(t), klim = tile_limit(t);
         unsigned char* kd = k_s + buf * BN * D * 2;
         unsigned char* vd = v_s + buf * BN * D * 2;
 #pragma unroll
         for (int i = tid; i < BN * CH; i += THREADS) {
             const int r = i / CH, ch = i % CH;
             const int kpos = kb + r;
-            const bool ok = kpos < kend;
+            const bool ok = kpos < klim;
             const int page = ok ? table[kpos >> page_shift] : 0;
             const __nv_bfloat16* src = kv_head + (size_t)page * page_stride + (((ok ? kpos : 0) & page_mask) * D + ch * 8);
             const uint32_t off = swz<D>(r, ch);
@@ -203,7 +210,7 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
     if (DECODE) {
 #pragma unroll
         for (int st = 0; st < STAGES - 1; ++st) {
-            if (st < ntiles && kbeg + (st + 1) * BN <= pos0 && early == st) {
+            if (st < ntiles && (st < ftiles || tile_base(st) + BN <= pos0) && early == st) {
                 load_tile(st, st);
                 cp_async_commit();
                 ++early;
@@ -432,7 +439,7 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
         cp_async_commit();
         const unsigned char* kt = k_s + buf * BN * D * 2;
         const unsigned char* vt = v_s + buf * BN * D * 2;
-        const int kb = kbeg + t * BN;
+        const int kb = tile_base(t), klim = tile_limit(t);
         const int key0 = DECODE ? warp * 16 : 0;            // first key of this warp's share of the tile
 
         // ---- s = q . k^T -------------------------------------------------------------------
@@ -461,7 +468,7 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
 
         // ---- mask (boundary tiles only), running maximum and sum ----------------------------------
         const int q_first = DECODE ? pos0 : pos0 + warp * 16, q_last = DECODE ? pos0 : q_first + 15;
-        const bool need_mask = kb + BN > kend || kb + BN - 1 > q_first || (a.window > 0 && kb <= q_last - a.window);
+        const bool need_mask = kb + BN > klim || kb + BN - 1 > q_first || (a.window > 0 && kb <= q_last - a.window);
         float mx_lo = -INFINITY, mx_hi = -INFINITY;
         if (need_mask) {
 #pragma unroll
@@ -470,7 +477,7 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
                 for (int e = 0; e < 4; ++e) {
                     const int kpos = kb + key0 + j * 8 + 2 * c + (e & 1);
                     const int qpos = (e < 2) ? qpos_lo : qpos_hi;
-                    const bool seen = kpos < kend && kpos <= qpos && (a.window <= 0 || kpos > qpos - a.window);
+                    const bool seen = kpos < klim && kpos <= qpos && (a.window <= 0 || kpos > qpos - a.window || kpos < a.keep_first);
                     if (!seen) s[j][e] = -INFINITY;
                 }
             }
@@ -821,7 +828,7 @@ LILY_API int lily_attention_prefill_mma(const void* q, const void* kv, void* out
                                         int bt_stride, const int* cu_seqlens, const int* prefix_lens,
                                         const int* tile_req, const int* tile_start, int tiles, int nq, int nkv,
                                         int d, int page_size, int window, float scale, float softcap,
-                                        cudaStream_t stream) {
+                                        int keep_first, cudaStream_t stream) {
     if (tiles == 0) return 0;
     LILY_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_prefill: %d query heads over %d kv heads", nq, nkv);
     LILY_REQUIRE(nq <= 65535 && page_size > 0, "attention_prefill: nq=%d page_size=%d", nq, page_size);
@@ -830,6 +837,7 @@ LILY_API int lily_attention_prefill_mma(const void* q, const void* kv, void* out
     a.cu_seqlens = cu_seqlens; a.prefix_lens = prefix_lens; a.tile_req = tile_req; a.tile_start = tile_start;
     a.splits = 1; a.nq = nq; a.nkv = nkv; a.d = d; a.page_size = page_size; a.window = window; a.scale = scale;
     a.softcap = softcap;
+    a.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
     bool merged = false;
     int rc = mma::dispatch<false>(a, dim3(tiles, nq), stream, &merged);
     if (rc) return rc;
@@ -885,9 +893,10 @@ static int decode_mma(AttnArgs& a, const void* q, const void* kv, void* out, con
 LILY_API int lily_attention_decode_mma(const void* q, const void* kv, void* out, const int* block_table,
                                        int bt_stride, const int* seq_lens, float* scratch, int requests, int splits,
                                        int nq, int nkv, int d, int page_size, int window, float scale, int stages,
-                                       float softcap, cudaStream_t stream) {
+                                       float softcap, int keep_first, cudaStream_t stream) {
     AttnArgs a{};
     a.softcap = softcap;
+    a.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
     return decode_mma(a, q, kv, out, block_table, bt_stride, seq_lens, scratch, requests, splits, nq, nkv, d, page_size,
                       window, scale, stages, stream);
 }

@@ -99,6 +99,7 @@ struct Params {
     const int* tile_start;
     __nv_bfloat16* out;
     int bt_stride, tiles, nq, nkv, page_size, window;
+    int keep_first;                       // with a window: keys at positions below this stay visible whatever the distance
     float scale_log2;                     // softmax scale times log2(e) (log2(e) alone under a cap)
     float cap, cap_in;                    // cap > 0: scores become cap * tanh(score * cap_in), cap_in = scale / cap
 };
@@ -289,7 +290,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int kv_end = pos0 + rows_valid;                // keys the last row sees, exclusive
     const int k_lo = (p.window > 0 && pos0 + 1 > p.window) ? pos0 + 1 - p.window : 0;
     const int jt0 = k_lo / BKV;
-    const int n = (kv_end - 1) / BKV - jt0 + 1;          // key tiles of this block (>= 1)
+    // the key tiles that hold kept first positions and lie wholly before the window's come first
+    const int ft = (p.window > 0 && p.keep_first > 0) ? min((p.keep_first + BKV - 1) / BKV, jt0) : 0;
+    const int n = ft + (kv_end - 1) / BKV - jt0 + 1;     // key tiles of this block (>= 1)
+    auto key_tile = [&](int j) { return j < ft ? j : jt0 + j - ft; };
 
     if (warp == 0) {
         if (lane == 0) {
@@ -304,7 +308,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 const uint32_t par = (uint32_t)((j / STAGES) & 1);
                 int page[2], off[2];
                 for (int h = 0; h < 2; ++h) {            // the two 64-key boxes of the tile
-                    const int key = (jt0 + j) * BKV + 64 * h;
+                    const int key = key_tile(j) * BKV + 64 * h;
                     const bool held = key < kv_end;
                     page[h] = held ? table[key / p.page_size] : 0;
                     off[h] = held ? key % p.page_size : 0;
@@ -448,13 +452,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 for (int c = 0; c < COLS; ++c) s[c] = p.cap * tanh_fast(s[c] * p.cap_in);
             }
             FA_TOC(10 + (part & 1), row == 0);
-            const int kb = (jt0 + j) * BKV + part * COLS;
+            const int kb = key_tile(j) * BKV + part * COLS;
             const bool need_mask = kb + COLS - 1 > pos0 || (p.window > 0 && kb <= pos0 + BQ - 1 - p.window);
             if (need_mask) {
 #pragma unroll
                 for (int c = 0; c < COLS; ++c) {
                     const int key = kb + c;
-                    const bool seen = key <= pos && (p.window <= 0 || key > pos - p.window);
+                    const bool seen = key <= pos && (p.window <= 0 || key > pos - p.window || key < p.keep_first);
                     s[c] = seen ? s[c] : -INFINITY;
                 }
             }
@@ -655,7 +659,9 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
     const int kv_end = pos0 + rows_valid;
     const int k_lo = (p.window > 0 && pos0 + 1 > p.window) ? pos0 + 1 - p.window : 0;
     const int jt0 = k_lo / BKV;
-    const int n = (kv_end - 1) / BKV - jt0 + 1;
+    const int ft = (p.window > 0 && p.keep_first > 0) ? min((p.keep_first + BKV - 1) / BKV, jt0) : 0;
+    const int n = ft + (kv_end - 1) / BKV - jt0 + 1;
+    auto key_tile = [&](int j) { return j < ft ? j : jt0 + j - ft; };
 
     if (warp == 0) {
         if (lane == 0) {
@@ -672,7 +678,7 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 const uint32_t par = (uint32_t)((j / KV2) & 1);
                 int page[2], off[2];
                 for (int h = 0; h < 2; ++h) {            // the two 64-key boxes of the tile
-                    const int key = (jt0 + j) * BKV + 64 * h;
+                    const int key = key_tile(j) * BKV + 64 * h;
                     const bool held = key < kv_end;
                     page[h] = held ? table[key / p.page_size] : 0;
                     off[h] = held ? key % p.page_size : 0;
@@ -790,7 +796,7 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
             if (!ok) break;
             FA_TIC();
             tc_fence_after();
-            const int kb = (jt0 + j) * BKV;
+            const int kb = key_tile(j) * BKV;
             const bool need_mask = kb + BKV - 1 > pos0 || (p.window > 0 && kb <= pos0 + BQ - 1 - p.window);
             // first pass: the row's maximum
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -807,7 +813,7 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
 #pragma unroll
                     for (int e = 0; e < 32; ++e) {
                         const int key = kb + c * 32 + e;
-                        const bool seen = key <= pos && (p.window <= 0 || key > pos - p.window);
+                        const bool seen = key <= pos && (p.window <= 0 || key > pos - p.window || key < p.keep_first);
                         s[e] = seen ? s[e] : -INFINITY;
                     }
                 }
@@ -857,7 +863,7 @@ attention_prefill_tc2_kernel(const __grid_constant__ CUtensorMap map_q, const __
 #pragma unroll
                     for (int e = 0; e < 32; ++e) {
                         const int key = kb + c * 32 + e;
-                        const bool seen = key <= pos && (p.window <= 0 || key > pos - p.window);
+                        const bool seen = key <= pos && (p.window <= 0 || key > pos - p.window || key < p.keep_first);
                         s[e] = seen ? s[e] : -INFINITY;
                     }
                 }
@@ -986,7 +992,7 @@ LILY_API int lily_attention_prefill_tc(const void* q, const void* kv, void* out,
                                        const int* cu_seqlens, const int* prefix_lens, const int* tile_req,
                                        const int* tile_start, int tiles, int nq, int nkv, int d, int page_size, int window,
                                        float scale, int tokens, int num_pages, int heads_per_block, float softcap,
-                                       cudaStream_t stream) {
+                                       int keep_first, cudaStream_t stream) {
     if (tiles == 0) return 0;
     LILY_REQUIRE(lily_attention_prefill_tc_takes(d, page_size), "attention_prefill_tc: head size %d, page size %d (takes 64 or 128, and multiples of 64)",
                  d, page_size);
@@ -1020,6 +1026,7 @@ LILY_API int lily_attention_prefill_tc(const void* q, const void* kv, void* out,
     p.block_table = block_table; p.cu_seqlens = cu_seqlens; p.prefix_lens = prefix_lens; p.tile_req = tile_req;
     p.tile_start = tile_start; p.out = (__nv_bfloat16*)out; p.bt_stride = bt_stride; p.tiles = tiles; p.nq = nq; p.nkv = nkv;
     p.page_size = page_size; p.window = window;
+    p.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
     p.cap = softcap > 0.f ? softcap : 0.f;
     p.cap_in = softcap > 0.f ? scale / softcap : 0.f;
     p.scale_log2 = (softcap > 0.f ? 1.f : scale) * 1.4426950408889634f;

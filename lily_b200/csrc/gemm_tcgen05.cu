@@ -45,7 +45,17 @@ constexpr uint32_t SPIN_LIMIT = 1u << 24;     // ~ a second of polling before a 
 
 __device__ int g_status = 0;                  // 0 ok; else (code << 16 | block) of the first wait that gave up
 
-enum Epilogue : int { kPlain = 0, kSiluMul = 1, kGeluMul = 2 };     // 2: the tanh form of GELU in place of SiLU
+enum Epilogue : int { kPlain = 0, kSiluMul = 1, kGeluMul = 2,       // 2: the tanh form of GELU in place of SiLU
+                      kActSilu = 3, kActGelu = 4, kActRelu2 = 5 };  // the plain product with an activation on every output
+
+// The activation of the plain epilogues 3 to 5 (SiLU, the tanh form of GELU, the square of max(., 0)); else the identity.
+template <int EPI>
+__device__ __forceinline__ float plain_act(float z) {
+    if (EPI == kActRelu2) { const float r = fmaxf(z, 0.f); return r * r; }
+    if (EPI == kActSilu) return __fdividef(z, 1.f + __expf(-z));
+    if (EPI == kActGelu) return __fdividef(z, 1.f + __expf(-1.5957691216057308f * (z + 0.044715f * z * z * z)));
+    return z;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -116,7 +126,7 @@ template <int EPI>
 __device__ __forceinline__ void epilogue_tile(uint32_t tbase, __nv_bfloat16* __restrict__ C,
                                               const __nv_bfloat16* __restrict__ bias, int row, int m_ok, int n0, int N,
                                               int ldc, int half) {
-    if (EPI == kPlain) {
+    if (EPI == kPlain || EPI >= kActSilu) {
 #pragma unroll 1
         for (int cc = half * (BN / 64); cc < (half + 1) * (BN / 64); ++cc) {   // this warp's half of the columns
             uint32_t r[32];
@@ -130,13 +140,13 @@ __device__ __forceinline__ void epilogue_tile(uint32_t tbase, __nv_bfloat16* __r
                         float f[8];
 #pragma unroll
                         for (int e = 0; e < 8; ++e)
-                            f[e] = __uint_as_float(r[v * 8 + e]) + (bias ? __bfloat162float(bias[col + v * 8 + e]) : 0.f);
+                            f[e] = plain_act<EPI>(__uint_as_float(r[v * 8 + e]) + (bias ? __bfloat162float(bias[col + v * 8 + e]) : 0.f));
                         *reinterpret_cast<uint4*>(dst + v * 8) =
                             make_uint4(pack2(f[0], f[1]), pack2(f[2], f[3]), pack2(f[4], f[5]), pack2(f[6], f[7]));
                     }
                 } else {
                     for (int e = 0; e < 32 && col + e < N; ++e)
-                        dst[e] = __float2bfloat16_rn(__uint_as_float(r[e]) + (bias ? __bfloat162float(bias[col + e]) : 0.f));
+                        dst[e] = __float2bfloat16_rn(plain_act<EPI>(__uint_as_float(r[e]) + (bias ? __bfloat162float(bias[col + e]) : 0.f)));
                 }
             }
         }
@@ -570,7 +580,8 @@ LILY_API int lily_gemm_tc_status() {
 }
 
 // epilogue 0: C [M, N] = A . B^T (+ bias [N]).  epilogue 1: C [M, N / 2] = silu(gate) * up where the
-// rows of B alternate between 128 gate rows and the 128 up rows of the same outputs (N % 256 == 0).
+// rows of B alternate between 128 gate rows and the 128 up rows of the same outputs (N % 256 == 0); 2: the same with
+// the tanh form of GELU.  epilogues 3, 4, 5: C [M, N] = act(A . B^T (+ bias)), act = SiLU, GELU (tanh form), relu(.)^2.
 LILY_API int lily_gemm_tc(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldc,
                           int epilogue, cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
@@ -582,8 +593,12 @@ LILY_API int lily_gemm_tc(const void* A, const void* B, void* C, const void* bia
         rc = epilogue == tc::kSiluMul ? tc::launch<tc::kSiluMul>(A, B, C, nullptr, M, N, K, lda, ldc, stream)
                                       : tc::launch<tc::kGeluMul>(A, B, C, nullptr, M, N, K, lda, ldc, stream);
     } else {
-        LILY_REQUIRE(epilogue == tc::kPlain && ldc >= N, "gemm_tc: epilogue %d, ldc %d", epilogue, ldc);
-        rc = tc::launch<tc::kPlain>(A, B, C, bias, M, N, K, lda, ldc, stream);
+        LILY_REQUIRE((epilogue == tc::kPlain || (epilogue >= tc::kActSilu && epilogue <= tc::kActRelu2)) && ldc >= N,
+                     "gemm_tc: epilogue %d, ldc %d", epilogue, ldc);
+        rc = epilogue == tc::kPlain     ? tc::launch<tc::kPlain>(A, B, C, bias, M, N, K, lda, ldc, stream)
+             : epilogue == tc::kActSilu ? tc::launch<tc::kActSilu>(A, B, C, bias, M, N, K, lda, ldc, stream)
+             : epilogue == tc::kActGelu ? tc::launch<tc::kActGelu>(A, B, C, bias, M, N, K, lda, ldc, stream)
+                                        : tc::launch<tc::kActRelu2>(A, B, C, bias, M, N, K, lda, ldc, stream);
     }
     if (rc) return rc;
     LILY_CHECK_LAUNCH("gemm_tc");

@@ -38,9 +38,9 @@ _SIGNATURES = {
     "lily_attention_prefill_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _i, _vp],
     "lily_attention_decode_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _i, _vp],
     "lily_attention_combine": [_vp, _vp, _i, _i, _i, _i, _i, _vp],
-    "lily_attention_prefill_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _vp],
-    "lily_attention_prefill_tc": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _f, _vp],
-    "lily_attention_decode_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _vp],
+    "lily_attention_prefill_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _i, _vp],
+    "lily_attention_prefill_tc": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _f, _i, _vp],
+    "lily_attention_decode_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _vp],
     "lily_attention_decode_mma_fused": [_vp, _i, _sz, _i, _vp, _vp, _i, _f, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _vp, _vp,
                                         _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _vp],
     "lily_sigmoid_gate": [_vp, _i, _vp, _i, _i, _sz, _sz, _vp],
@@ -411,11 +411,12 @@ def gemm_tc_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 
 def gemm_tc(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
-            silu_mul_block: bool = False, activation: str = "silu") -> torch.Tensor:
+            silu_mul_block: bool = False, activation: str = "silu", plain_activation: Optional[str] = None) -> torch.Tensor:
     """``x [M, K] . weight [N, K]^T`` in bfloat16 on the tcgen05 tensor cores (TMA-fed, accumulator
     in tensor memory).  With ``silu_mul_block`` the rows of ``weight`` alternate between 128 gate
     rows and the 128 up rows of the same outputs and the result is ``act(gate) * up`` [M, N / 2]
-    (``activation``: "silu" or "gelu_tanh")."""
+    (``activation``: "silu" or "gelu_tanh").  ``plain_activation`` ("silu", "gelu_tanh", "relu2"): the plain product
+    with that activation on every output, applied to the float32 sums in the epilogue."""
     _dev(x, weight, bias)
     m, k = x.shape
     n = weight.shape[0]
@@ -423,7 +424,8 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] 
         raise KernelError(f"gemm_tc: x {tuple(x.shape)} {x.dtype} against weight {tuple(weight.shape)} {weight.dtype}")
     out = torch.empty((m, n // 2 if silu_mul_block else n), dtype=torch.bfloat16, device=x.device)
     _call("lily_gemm_tc", _p(x), _p(weight), _p(out), _p(bias), m, n, k, k, out.shape[1],
-          1 + ACTIVATIONS[activation] if silu_mul_block else 0, _stream())
+          1 + ACTIVATIONS[activation] if silu_mul_block else (3 + PLAIN_ACTIVATIONS[plain_activation] if plain_activation else 0),
+          _stream())
     return out
 
 
@@ -569,7 +571,7 @@ def prefill_tile_rows(dtype: torch.dtype = torch.float32, d: int = 0, page_size:
     lib = library()
     if values_in_keys and heads and latent_tensor_cores(dtype, d, dv, softcap=softcap):
         return int(lib.lily_latent_attention_mma_tile_tokens(int(heads)))
-    same = (dv is None or dv == d) and not values_in_keys and not keep_first
+    same = (dv is None or dv == d) and not values_in_keys
     if same and uses_tcgen05_attention(dtype, d, page_size, new_tokens):
         return int(lib.lily_attention_prefill_tc_rows())
     return int(lib.lily_attention_prefill_mma_rows() if same and uses_tensor_cores(dtype, d) else lib.lily_attention_prefill_simt_rows())
@@ -587,7 +589,7 @@ def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torc
                       dv: Optional[int] = None, values_in_keys: bool = False, keep_first: int = 0) -> None:
     """Causal attention of each request's new tokens over its cached prefix and themselves.  ``softcap``: scores
     become softcap * tanh(score * scale / softcap) before the softmax; ``keep_first``: beside a window, keys at
-    positions below this stay visible (CUDA-core kernels); ``dv``: the
+    positions below this stay visible; ``dv``: the
     value head size where it differs from d (CUDA-core kernels; ``out`` is then [tokens, nq * dv]).
     ``values_in_keys``: the values are the first ``dv`` columns of the key rows and a page holds keys only (CUDA-core kernels).
     ``q`` and ``out`` are [tokens, nq * d] indexed by ``cu_seqlens``; tiles list (request, offset)
@@ -611,18 +613,18 @@ def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torc
               page_size, int(window or 0), float(scale), _stream())
         return
     keep_first = int(keep_first or 0) if window else 0
-    tensor_cores = dv == d and not values_in_keys and not keep_first and uses_tensor_cores(q.dtype, d)
+    tensor_cores = dv == d and not values_in_keys and uses_tensor_cores(q.dtype, d)
     base_rows = int(lib.lily_attention_prefill_mma_rows() if tensor_cores else lib.lily_attention_prefill_simt_rows())
     if tile_rows is not None and tile_rows != base_rows:
         if not (tile_rows == int(lib.lily_attention_prefill_tc_rows()) and q.dtype == torch.bfloat16 and dv == d
-                and not keep_first and lib.lily_attention_prefill_tc_takes(int(d), int(page_size))):
+                and lib.lily_attention_prefill_tc_takes(int(d), int(page_size))):
             raise KernelError(f"attention_prefill: no kernel with tiles of {tile_rows} rows for {q.dtype}, head size {d}, "
                               f"page size {page_size}")
         if not (q.is_contiguous() and out.is_contiguous() and kv_layer.is_contiguous()):
             raise KernelError("attention_prefill: the tcgen05 kernel takes contiguous q, out and cache")
-        _call("lily_attention_prefill_tc", *common, q.shape[0], kv_layer.shape[0], int(heads_per_block), cap, _stream())
+        _call("lily_attention_prefill_tc", *common, q.shape[0], kv_layer.shape[0], int(heads_per_block), cap, keep_first, _stream())
     elif tensor_cores:
-        _call("lily_attention_prefill_mma", *common, cap, _stream())
+        _call("lily_attention_prefill_mma", *common, cap, keep_first, _stream())
     else:
         _call("lily_attention_prefill_simt", *common, _dt(q), cap, -dv if values_in_keys else dv, keep_first, _stream())
 
@@ -663,8 +665,8 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
               int(window or 0), float(scale), _stream())
         if splits > 1:
             _call("lily_attention_combine", _p(scratch), _p(out), requests, nq, dv, splits, _dt(q), _stream())
-    elif dv == d and not values_in_keys and not (keep_first and window) and uses_tensor_cores(q.dtype, d):
-        _call("lily_attention_decode_mma", *common, int(stages), cap, _stream())   # merges the splits itself (cluster, or combine behind)
+    elif dv == d and not values_in_keys and uses_tensor_cores(q.dtype, d):
+        _call("lily_attention_decode_mma", *common, int(stages), cap, int(keep_first or 0) if window else 0, _stream())   # merges the splits itself (cluster, or combine behind)
         if splits > 1 and (stages or requests * nkv * -(-(nq // nkv) // 16) > decode_clusters(d, splits, nq // nkv)):
             launches["count"] += 1                                   # the combine kernel, launched inside
     else:
@@ -759,7 +761,8 @@ def plan_decode_attention(dtype: torch.dtype, requests: int, nq: int, nkv: int, 
     blocks are resident at once (three a SM) and more when they run in several rounds (measured at batch 64:
     2 % of the step).
     ``fusable`` False: the caller prepares queries and cache itself (something stands between its projection and
-    the attention); ``keep_first``: the window keeps the first positions in sight (CUDA-core kernel).
+    the attention); ``keep_first``: the window keeps the first positions in sight (the caller then prepares queries
+    and cache itself as well).
     ``even``: the caller knows that the rows are about equally long (the longest at most an eighth over their
     mean).  Then, and when ``whole_rows_pay``, a block
     takes all keys of its row with three stages; rows of very different lengths keep their ranges, which spread a
@@ -768,7 +771,8 @@ def plan_decode_attention(dtype: torch.dtype, requests: int, nq: int, nkv: int, 
         return DecodePlan(1, False, 0, "single")
     group = nq // nkv
     dv = int(dv or d)
-    tensor_cores = dv == d and not values_in_keys and not keep_first and uses_tensor_cores(dtype, d)      # values of another head size run on CUDA cores
+    tensor_cores = dv == d and not values_in_keys and uses_tensor_cores(dtype, d)      # values of another head size run on CUDA cores
+    fusable = fusable and not keep_first          # the kernel that takes the projection itself has no kept first positions
     row_blocks = -(-group // 16)                 # the tensor-core kernel takes 16 query heads of a kv head a block
     pairs = requests * nkv * row_blocks
     if even and tensor_cores and d <= 128 and _WHOLE_ROWS and whole_rows_pay(pairs, sm_count()):
@@ -1431,6 +1435,8 @@ def top_logprobs(logits: torch.Tensor, k: torch.Tensor):
 # ------------------------------------------------------------------------------ norms on both sides of a sublayer, plain feed-forward
 
 PLAIN_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu2": 2}
+# LILY_B200_FUSED_ACTIVATION=0 keeps the plain feed-forward's activation a pass of its own behind the library product
+_FUSED_ACTIVATION = os.environ.get("LILY_B200_FUSED_ACTIVATION", "1") != "0"
 
 
 def add_normed_rmsnorm(resid: torch.Tensor, delta: torch.Tensor, post_gain: torch.Tensor, post_eps: float, mult: float,
@@ -1475,8 +1481,13 @@ def activation(x: torch.Tensor, out_dtype: torch.dtype, activation: str = "relu2
 
 
 def linear_activation(x: torch.Tensor, weight: torch.Tensor, activation_name: str = "relu2") -> torch.Tensor:
-    """``act(x @ weight.T)`` in ``x``'s dtype: the product (whole, or float32 partial sums for a few tokens) with the
-    activation as a pass over it."""
+    """``act(x @ weight.T)`` in ``x``'s dtype: for 65 tokens and more in bfloat16 the tcgen05 product with the activation
+    in its epilogue (where ``gate_up_fused_pays``: the [tokens, N] intermediate is never written); else the product
+    (whole, or float32 partial sums for a few tokens) with the activation as a pass over it."""
+    if activation_name not in PLAIN_ACTIVATIONS:
+        raise KernelError(f"no activation {activation_name!r}; have {sorted(PLAIN_ACTIVATIONS)}")
+    if _FUSED_ACTIVATION and gate_up_fused_pays(x.shape[0], weight.shape[0]) and gemm_tc_takes(x, weight) and weight.is_contiguous():
+        return gemm_tc(x, weight, plain_activation=activation_name)
     return activation(linear_auto(x, weight), x.dtype, activation_name)
 
 

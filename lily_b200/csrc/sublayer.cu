@@ -86,6 +86,68 @@ __global__ void add_normed_rmsnorm_kernel(const NormedAddArgs a) {
         dst[i] = from_float<T>((row[i] * inv) * gain_at(a.weight, a.weight_bf16, i));
 }
 
+// Sum over the block with one barrier: every thread adds the warps' sums in the same order.  `slots` holds a float per
+// warp and is not used again before the next barrier of the block.
+__device__ __forceinline__ float block_sum_once(float v, float* slots) {
+    v = warp_sum(v);
+    if ((threadIdx.x & 31) == 0) slots[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += slots[w];
+    return t;
+}
+
+template <typename T> __device__ __forceinline__ void store_four(T* dst, float4 v);
+template <> __device__ __forceinline__ void store_four<float>(float* dst, float4 v) { *reinterpret_cast<float4*>(dst) = v; }
+template <> __device__ __forceinline__ void store_four<__nv_bfloat16>(__nv_bfloat16* dst, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 w;
+    w.x = *reinterpret_cast<const uint32_t*>(&lo);
+    w.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(dst) = w;
+}
+
+// One block per output row with the row in registers: PER pieces of four columns a thread (hidden = 4 * PER * threads),
+// a barrier per sum of squares, outputs stored four at a time.  Bases 16-byte aligned.
+template <typename T, int PER>
+__global__ void add_normed_rmsnorm_reg_kernel(const NormedAddArgs a) {
+    __shared__ float slots[2][32];
+    pdl_enter_small();
+    const int m = blockIdx.x, hidden = a.hidden;
+    const size_t src = (size_t)(a.rows ? a.rows[m] : m) * hidden;
+    float4 d[PER], v[PER];
+    float ssq = 0.f;
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+        const int i = (k * blockDim.x + threadIdx.x) * 4;
+        d[k] = a.delta.four(src + i);
+        v[k] = *reinterpret_cast<const float4*>(a.resid + src + i);
+        ssq += d[k].x * d[k].x + d[k].y * d[k].y + d[k].z * d[k].z + d[k].w * d[k].w;
+    }
+    const float inv_d = rsqrtf(block_sum_once(ssq, slots[0]) / (float)hidden + a.post_eps);
+    ssq = 0.f;
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+        const int i = (k * blockDim.x + threadIdx.x) * 4;
+        const float4 g = *reinterpret_cast<const float4*>(a.post_gain + i);
+        v[k].x += a.mult * ((d[k].x * inv_d) * g.x);
+        v[k].y += a.mult * ((d[k].y * inv_d) * g.y);
+        v[k].z += a.mult * ((d[k].z * inv_d) * g.z);
+        v[k].w += a.mult * ((d[k].w * inv_d) * g.w);
+        if (a.write_residual) *reinterpret_cast<float4*>(a.resid + src + i) = v[k];
+        ssq += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+    }
+    if (a.weight == nullptr) return;
+    const float inv = rsqrtf(block_sum_once(ssq, slots[1]) / (float)hidden + a.eps);
+    T* dst = (T*)a.out + (size_t)m * hidden;
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+        const int i = (k * blockDim.x + threadIdx.x) * 4;
+        store_four<T>(dst + i, make_float4((v[k].x * inv) * gain_at(a.weight, a.weight_bf16, i), (v[k].y * inv) * gain_at(a.weight, a.weight_bf16, i + 1),
+                                           (v[k].z * inv) * gain_at(a.weight, a.weight_bf16, i + 2), (v[k].w * inv) * gain_at(a.weight, a.weight_bf16, i + 3)));
+    }
+}
+
 // The same for a few rows: a cluster of CL blocks shares a row, each block takes hidden / CL columns (four a thread)
 // and the blocks exchange their two sums of squares through distributed shared memory, so that 8 rows keep 64 SMs
 // busy instead of 8.  grid (CL, rows), cluster (CL, 1, 1); hidden % (4 * CL) == 0; block = hidden / (4 * CL) threads.
@@ -203,6 +265,26 @@ LILY_API int lily_add_normed_rmsnorm(float* resid, const void* delta, int delta_
                                            : cudaLaunchKernelEx(&cfg, add_normed_rmsnorm_cluster_kernel<float, CL>, a);
         if (e != cudaSuccess) { set_error("add_normed_rmsnorm: launch failed: %s", cudaGetErrorString(e)); return 2; }
         return 0;
+    }
+    // whole rows in registers: 32 to 256 threads with 1, 2, 4 or 8 pieces of four columns each
+    if (vec && ((uintptr_t)out & 15) == 0) {
+        int t = 0, per = 0;
+        for (int threads = 256; threads >= 32 && !per; threads /= 2)
+            for (int pieces = 1; pieces <= 8 && !per; pieces *= 2)
+                if (hidden == 4 * threads * pieces) { t = threads; per = pieces; }
+        if (per == 1 || per == 2 || per == 4 || per == 8) {
+#define REG(T)                                                                                        \
+            do {                                                                                      \
+                if (per == 1) launch_pdl(add_normed_rmsnorm_reg_kernel<T, 1>, dim3(n_out), dim3(t), 0, stream, a);       \
+                else if (per == 2) launch_pdl(add_normed_rmsnorm_reg_kernel<T, 2>, dim3(n_out), dim3(t), 0, stream, a);  \
+                else if (per == 4) launch_pdl(add_normed_rmsnorm_reg_kernel<T, 4>, dim3(n_out), dim3(t), 0, stream, a);  \
+                else launch_pdl(add_normed_rmsnorm_reg_kernel<T, 8>, dim3(n_out), dim3(t), 0, stream, a);                \
+            } while (0)
+            if (out_dtype == kBF16) REG(__nv_bfloat16); else REG(float);
+#undef REG
+            LILY_CHECK_LAUNCH("add_normed_rmsnorm");
+            return 0;
+        }
     }
     const size_t smem = sizeof(float) * (40 + (size_t)hidden);
     int threads = vec ? (hidden / 4 + 31) / 32 * 32 : (hidden + 31) / 32 * 32;

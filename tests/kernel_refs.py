@@ -200,8 +200,10 @@ def gemm_tc_takes(x, weight):
     return x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
 
 
-def gemm_tc(x, weight, bias=None, silu_mul_block=False, activation="silu"):
+def gemm_tc(x, weight, bias=None, silu_mul_block=False, activation="silu", plain_activation=None):
     out = linear(x, weight, bias, out_dtype=torch.float32)
+    if plain_activation:
+        return _activate(out, plain_activation).to(x.dtype)
     return silu_mul(out, x.dtype, block=128, activation=activation) if silu_mul_block else out.to(x.dtype)
 
 

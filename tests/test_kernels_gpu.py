@@ -205,6 +205,27 @@ def test_gemm_tcgen05(m, n, k):
     assert torch.equal(o.gemm_tc(x, w), got) and o.gemm_tc_status() == 0          # again: the same bits
 
 
+@pytest.mark.parametrize("activation", ["relu2", "silu", "gelu_tanh"])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (2048, 3072, 2048), (300, 1000, 136), (65, 331, 200), (777, 520, 4096)])
+def test_gemm_tcgen05_activation_epilogue(activation, m, n, k):
+    """The plain product with an activation on the float32 sums before they are rounded, and the feed-forward's
+    ``linear_activation`` that takes this kernel for 65 tokens and more."""
+    o = ops()
+    g = torch.Generator(device=DEV).manual_seed(15)
+    x = (torch.randn(m, k, device=DEV, generator=g) * 0.5).bfloat16()
+    w = (torch.randn(n, k, device=DEV, generator=g) * (k ** -0.5) * 2).bfloat16()
+    z = x.float() @ w.float().t()
+    want = {"relu2": torch.clamp(z, min=0) ** 2, "silu": torch.nn.functional.silu(z),
+            "gelu_tanh": torch.nn.functional.gelu(z, approximate="tanh")}[activation]
+    got = o.gemm_tc(x, w, plain_activation=activation)
+    assert o.gemm_tc_status() == 0 and got.shape == (m, n)
+    torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
+    via = o.linear_activation(x, w, activation)
+    torch.testing.assert_close(via.float(), want, atol=2e-2, rtol=2e-2)
+    unfused = o.activation(o.linear(x, w, out_dtype=torch.float32), torch.bfloat16, activation)
+    torch.testing.assert_close(unfused.float(), want, atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("m,inter,k", [(128, 128, 64), (2048, 12288, 4096), (300, 384, 136), (70, 256, 4096)])
 def test_gemm_tcgen05_silu_mul_epilogue(m, inter, k):
     o = ops()

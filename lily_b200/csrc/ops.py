@@ -925,15 +925,17 @@ def causal_conv(proj: torch.Tensor, col0: int, channels: int, weight: torch.Tens
     _dev(proj, weight, bias, state, chunk_req, chunk_start, cu_seqlens, slots)
     n, width = proj.shape
     taps = weight.shape[1]
-    if weight.dtype != torch.float32 or tuple(weight.shape) != (channels, taps) or state.dtype != torch.float32:
+    if state is None and taps > 1:
+        raise KernelError("causal_conv: only a single tap carries nothing from step to step")
+    if weight.dtype != torch.float32 or tuple(weight.shape) != (channels, taps) or (state is not None and state.dtype != torch.float32):
         raise KernelError("causal_conv: float32 weights [channels, taps] and a float32 state")
     if bias is not None and (bias.dtype != torch.float32 or bias.numel() != channels):
         raise KernelError("causal_conv: the bias is float32 [channels]")
-    if state.dim() != 2 or state_off + (taps - 1) * channels > state.shape[1] or col0 + channels > width:
+    if col0 + channels > width or (state is not None and (state.dim() != 2 or state_off + (taps - 1) * channels > state.shape[1])):
         raise KernelError("causal_conv: columns or state out of range")
     out = torch.empty((n, channels), dtype=proj.dtype, device=proj.device)
     _call("lily_causal_conv", _p(proj), width, int(col0), int(channels), int(taps), _p(weight), _p(bias), _p(state),
-          state.shape[1], int(state_off), _p(out), _i32(chunk_req, "chunk_req"), _i32(chunk_start, "chunk_start"),
+          state.shape[1] if state is not None else 0, int(state_off), _p(out), _i32(chunk_req, "chunk_req"), _i32(chunk_start, "chunk_start"),
           chunk_req.numel(), int(chunk), _i32(cu_seqlens, "cu_seqlens"), _i32(slots, "slots"), _dt(proj),
           1 if activation == "silu" else 0, _stream())
     return out

@@ -59,7 +59,9 @@ VARIED = {"architecture": "Gotivik", "vocab": 131, "width": 48, "norm": {"eps": 
                      diff_attention(heads=3, kv_heads=1, dim=16, vdim=16, scale=0.2, diff=0.8, softcap=None, q_temp=None, ff=24),
                      conv_attention(heads=2, kv_heads=1, dim=8, vdim=8, conv=0, window=5, keep_first=0, rot_dims=0, ff=32),
                      conv_attention(heads=1, kv_heads=1, dim=24, vdim=16, conv=4, window=20, keep_first=17, rot_dims=24,
-                                    base=50.0, ff=32)]}
+                                    base=50.0, ff=32),
+                     # a single tap: a gain on every channel, nothing carried from step to step
+                     conv_attention(heads=2, kv_heads=1, dim=8, vdim=24, conv=1, window=7, keep_first=1, rot_dims=4, ff=None)]}
 
 # Sharp attention: a large scale puts nearly all weight on the best visible key, so a key that is wrongly seen or
 # wrongly dropped at a window's edge or among the kept first positions changes the output outright.

@@ -347,7 +347,10 @@ def causal_conv(proj, col0, channels, weight, bias, state, state_off, chunk_req,
         t0, t1 = int(cu_seqlens[r]), int(cu_seqlens[r + 1])
         if t1 == t0:
             continue
-        held = state[int(slots[r]), state_off:state_off + (taps - 1) * channels].view(taps - 1, channels)
+        if taps > 1:
+            held = state[int(slots[r]), state_off:state_off + (taps - 1) * channels].view(taps - 1, channels)
+        else:
+            held = torch.zeros((0, channels))                   # a single tap carries nothing from step to step
         seq = torch.cat([held, proj[t0:t1, col0:col0 + channels].float()])
         acc = (bias.float() if bias is not None else torch.zeros(channels))[None, :].expand(t1 - t0, channels).clone()
         for j in range(taps):

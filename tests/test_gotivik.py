@@ -192,11 +192,11 @@ def test_layers_that_share_tensors_have_caches_and_states_of_their_own():
         path = gm.write_model_dir(tmp + "/m", gm.VARIED, gm.make_weights(gm.VARIED, 3))
         runner = make_runner(path, max_tokens=64, page_size=8, max_requests=2, context_length=64)
         model = runner.model
-        assert len(model.blocks) == 6 and [e.block for e in model.spec.schedule] == [0, 1, 0, 2, 1, 2, 3, 4, 5]
+        assert len(model.blocks) == 7 and [e.block for e in model.spec.schedule] == [0, 1, 0, 2, 1, 2, 3, 4, 5, 6]
         needs = {(n.kv_heads, n.head_dim, n.v_head_dim, n.window, n.keep_first): layers for n, layers in model.cache_groups}
         assert needs == {(2, 16, 12, None, 0): 2, (3, 16, 8, 11, 3): 2, (2, 12, 20, None, 0): 2, (1, 32, 16, None, 0): 1,
-                         (1, 8, None, 5, 0): 1, (1, 24, 16, 20, 17): 1}
-        # the convolution's carried rows: (taps - 1) x (q + k + v channels), one state a run of a layer that has taps
+                         (1, 8, None, 5, 0): 1, (1, 24, 16, 20, 17): 1, (1, 8, 24, 7, 1): 1}
+        # the convolution's carried rows: (taps - 1) x (q + k + v channels), one state a run of a layer with two taps or more
         assert [tuple(s.shape[1:]) for s in runner.cache.states] == [(2 * (96 + 48 + 24),)] + [(1 * (24 + 24 + 40),)] + \
             [(2 * (96 + 48 + 24),)] + [(1 * (24 + 24 + 40),)] + [(3 * (24 + 24 + 16),)]
 

@@ -389,7 +389,7 @@ def test_add_with_a_norm_on_both_sides(device, out_dtype, width, tokens):
 
 @pytest.mark.parametrize("device", DEVICES)
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("tokens,cols", [(3, 40), (70, 384), (5, 1000), (33, 4099)])
+@pytest.mark.parametrize("tokens,cols", [(3, 40), (70, 392), (5, 1000), (33, 4099)])
 def test_squared_relu(device, dtype, tokens, cols):
     if device == "cpu" and dtype == torch.bfloat16:
         pytest.skip("one precision on the CPU")
@@ -403,7 +403,7 @@ def test_squared_relu(device, dtype, tokens, cols):
 
 
 @pytest.mark.parametrize("device", DEVICES)
-@pytest.mark.parametrize("width,ff,tokens", [(48, 40, 7), (128, 384, 3), (256, 200, 70)])
+@pytest.mark.parametrize("width,ff,tokens", [(48, 40, 7), (128, 392, 3), (256, 200, 70)])
 def test_feed_forward_part(device, width, ff, tokens):
     """The feed-forward part (product, squared ReLU, product) against ``down(relu(up h)^2)``."""
     from lily_b200.parts.base import BuildContext, build_part

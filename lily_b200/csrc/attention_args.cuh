@@ -38,6 +38,10 @@ struct AttnArgs {
                               // keys [kv_heads, page_size, d] followed by its values [kv_heads, page_size, dv]
     int v_in_k;               // CUDA-core kernels: the values are the first dv columns of the key rows; a page holds keys only
     int keep_first;           // with a window: keys at positions below this stay visible whatever the distance
+    int sink;                 // CUDA-core kernels: the softmax's denominator holds one more unit (a key of score 0 without a value)
+    int v_all;                // CUDA-core kernels: a query head is weighted over the values of every kv head, not only its own:
+                              // its output row is [nkv][dv] (the caller mixes heads afterwards); `dv` stays one head's size
+    int out_f32;              // CUDA-core kernels: outputs are written in float32 whatever the cache's dtype
     int stages;               // decode, tensor-core kernel: key/value tiles a block keeps in shared memory (0: the default, 2;
                               // 3: two blocks a SM instead of three, each with two tiles in flight; head sizes up to 128)
 };

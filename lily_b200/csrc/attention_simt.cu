@@ -7,6 +7,10 @@
 // size of their own (`dv`): a page is then its keys [kv_heads, page_size, d] followed by its values
 // [kv_heads, page_size, dv], and outputs have dv columns a head.  Or the values are the first dv columns of the key
 // rows themselves (`v_in_k`, attention over a cached latent that serves as key and value): a page is then its keys alone.
+// `sink`: a row's running (max, sum) start at (0, 1), a key of score 0 that has no value, so the weights are
+// exp(s_j) / (1 + sum exp(s_j)).  `v_all`: a query head's weights meet the values of every kv head at once (a value row
+// of nkv * dv columns gathered from the heads' tiles of the page), for callers that mix the heads' weights afterwards:
+// sum_g T[h][g] (P_g V_c) = (sum_g T[h][g] P_g) V_c.
 //
 //  * prefill: grid (query tiles, query heads).  A tile is up to 32 consecutive new tokens of one
 //    request; their keys are the request's cached prefix and the new tokens up to each query
@@ -36,7 +40,7 @@ template <typename T, int DCH, bool DECODE>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_simt_kernel(const AttnArgs a) {
     extern __shared__ float smem[];
-    const int d = a.d, dv = a.dv;
+    const int d = a.d, dv = a.v_all ? a.nkv * a.dv : a.dv;      // dv: the value columns a query row gathers
     float* Qs = smem;                          // [ROWS][d]
     float* Ks = Qs + ROWS * d;                 // [KEYS][d + 1]
     float* Vs = Ks + KEYS * (d + 1);           // [KEYS][dv] (none when the values are read out of the key rows)
@@ -110,14 +114,17 @@ attention_simt_kernel(const AttnArgs a) {
     float m[RPW], l[RPW], acc[RPW][DCH];
 #pragma unroll
     for (int i = 0; i < RPW; ++i) {
-        m[i] = -INFINITY;
-        l[i] = 0.f;
+        // the sink counts once a row: in the block of the first key range
+        const bool sunk = a.sink && (!DECODE || blockIdx.z == 0);
+        m[i] = sunk ? 0.f : -INFINITY;
+        l[i] = sunk ? 1.f : 0.f;
 #pragma unroll
         for (int c = 0; c < DCH; ++c) acc[i][c] = 0.f;
     }
 
     const int* table = a.block_table + (size_t)req * a.bt_stride;
-    const size_t khead = (size_t)a.page_size * d, vhead = a.v_in_k ? 0 : (size_t)a.page_size * dv;     // one head's tiles in a page
+    const int dv1 = a.dv;                                                                                // one head's value columns
+    const size_t khead = (size_t)a.page_size * d, vhead = a.v_in_k ? 0 : (size_t)a.page_size * dv1;     // one head's tiles in a page
     const size_t page_stride = (size_t)a.nkv * (khead + vhead);
     const float cap = a.softcap, cap_in = cap > 0.f ? a.scale / cap : 0.f;
 
@@ -131,9 +138,11 @@ attention_simt_kernel(const AttnArgs a) {
                 const int page = table[kpos / a.page_size];
                 const T* base = kv + (size_t)page * page_stride;
                 const T* ksrc = base + (size_t)kvh * khead + (size_t)(kpos % a.page_size) * d;
-                const T* vsrc = base + (size_t)a.nkv * khead + (size_t)kvh * vhead + (size_t)(kpos % a.page_size) * dv;
+                const T* vsrc = base + (size_t)a.nkv * khead + (size_t)(a.v_all ? 0 : kvh) * vhead + (size_t)(kpos % a.page_size) * dv1;
                 for (int c = lane; c < d; c += 32) Ks[j * (d + 1) + c] = to_float(ksrc[c]);
-                if (!a.v_in_k)
+                if (a.v_all)
+                    for (int c = lane; c < dv; c += 32) Vs[j * dv + c] = to_float(vsrc[(size_t)(c / dv1) * vhead + c % dv1]);
+                else if (!a.v_in_k)
                     for (int c = lane; c < dv; c += 32) Vs[j * dv + c] = to_float(vsrc[c]);
             } else {
                 for (int c = lane; c < d; c += 32) Ks[j * (d + 1) + c] = 0.f;
@@ -210,11 +219,14 @@ attention_simt_kernel(const AttnArgs a) {
             }
         } else {
             const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
-            T* dst = out + ((size_t)row_tok[i] * a.nq + row_head[i]) * dv;
+            const size_t at = ((size_t)row_tok[i] * a.nq + row_head[i]) * dv;
 #pragma unroll
             for (int c = 0; c < DCH; ++c) {
                 const int col = lane + 32 * c;
-                if (col < dv) dst[col] = from_float<T>(acc[i][c] * inv);
+                if (col < dv) {
+                    if (a.out_f32) ((float*)a.out)[at + col] = acc[i][c] * inv;
+                    else out[at + col] = from_float<T>(acc[i][c] * inv);
+                }
             }
         }
     }
@@ -309,8 +321,9 @@ static size_t smem_bytes(int d, int dv, int v_in_k) { return sizeof(float) * ((s
 
 template <typename T, bool DECODE>
 static int launch(const AttnArgs& a, dim3 grid, cudaStream_t stream) {
-    const int dch = (a.dv + 31) / 32;              // output columns a lane owns
-    const size_t smem = smem_bytes(a.d, a.dv, a.v_in_k);
+    const int dvo = a.v_all ? a.nkv * a.dv : a.dv;
+    const int dch = (dvo + 31) / 32;               // output columns a lane owns
+    const size_t smem = smem_bytes(a.d, dvo, a.v_in_k);
 #define CASE(N)                                                                                          \
     case N: {                                                                                            \
         auto kern = attention_simt_kernel<T, N, DECODE>;                                                 \
@@ -326,7 +339,7 @@ static int launch(const AttnArgs& a, dim3 grid, cudaStream_t stream) {
     switch (dch) {
         CASE(1) CASE(2) CASE(3) CASE(4) CASE(5) CASE(6) CASE(7) CASE(8) CASE(9) CASE(10) CASE(11) CASE(12) CASE(13) CASE(14) CASE(15) CASE(16)
         default:
-            set_error("attention: value head size %d is beyond the 512 this kernel takes", a.dv);
+            set_error("attention: %d value columns a row are beyond the 512 this kernel takes", dvo);
             return 1;
     }
 #undef CASE
@@ -342,6 +355,18 @@ static int check_common(const char* name, int nq, int nkv, int d, int page_size,
     return 0;
 }
 
+// `flags` of the launchers below
+constexpr int kSink = 1, kAllValues = 2, kOutF32 = 4;
+
+static int apply_flags(const char* name, AttnArgs& a, int flags) {
+    a.sink = (flags & kSink) != 0;
+    a.v_all = (flags & kAllValues) != 0;
+    a.out_f32 = (flags & kOutF32) != 0;
+    LILY_REQUIRE(!(a.v_all && a.v_in_k), "%s: values that are columns of the key rows belong to one shared head", name);
+    LILY_REQUIRE(!a.v_all || a.nkv * a.dv <= 512, "%s: %d kv heads of %d value columns are beyond the 512 a row may gather", name, a.nkv, a.dv);
+    return 0;
+}
+
 }  // namespace lily
 
 using namespace lily;
@@ -350,7 +375,7 @@ LILY_API int lily_attention_prefill_simt(const void* q, const void* kv, void* ou
                                          int bt_stride, const int* cu_seqlens, const int* prefix_lens,
                                          const int* tile_req, const int* tile_start, int tiles, int nq, int nkv,
                                          int d, int page_size, int window, float scale, int dtype,
-                                         float softcap, int dv, int keep_first, cudaStream_t stream) {
+                                         float softcap, int dv, int keep_first, int flags, cudaStream_t stream) {
     if (tiles == 0) return 0;
     if (check_common("attention_prefill", nq, nkv, d, page_size, dv)) return 1;
     LILY_REQUIRE(nq <= 65535, "attention_prefill: %d query heads", nq);
@@ -360,6 +385,7 @@ LILY_API int lily_attention_prefill_simt(const void* q, const void* kv, void* ou
     a.splits = 1; a.nq = nq; a.nkv = nkv; a.d = d; a.page_size = page_size; a.window = window; a.scale = scale;
     a.softcap = softcap; a.dv = dv > 0 ? dv : (dv < 0 ? -dv : d); a.v_in_k = dv < 0;
     a.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
+    if (apply_flags("attention_prefill", a, flags)) return 1;
     dim3 grid(tiles, nq);
     int rc = dtype == kBF16 ? launch<__nv_bfloat16, false>(a, grid, stream) : launch<float, false>(a, grid, stream);
     if (rc) return rc;
@@ -393,19 +419,21 @@ LILY_API size_t lily_attention_decode_scratch_floats(int requests, int nq, int d
 LILY_API int lily_attention_decode_simt(const void* q, const void* kv, void* out, const int* block_table,
                                         int bt_stride, const int* seq_lens, float* scratch, int requests,
                                         int splits, int nq, int nkv, int d, int page_size, int window,
-                                        float scale, int dtype, float softcap, int dv, int keep_first,
+                                        float scale, int dtype, float softcap, int dv, int keep_first, int flags,
                                         cudaStream_t stream) {
     if (requests == 0) return 0;
     if (check_common("attention_decode", nq, nkv, d, page_size, dv)) return 1;
-    const int d_out = dv > 0 ? dv : (dv < 0 ? -dv : d);
+    const int d_one = dv > 0 ? dv : (dv < 0 ? -dv : d);
+    const int d_out = (flags & kAllValues) ? nkv * d_one : d_one;
     LILY_REQUIRE(splits >= 1 && splits <= 65535, "attention_decode: %d splits", splits);
     LILY_REQUIRE(splits == 1 || scratch != nullptr, "attention_decode: splits need scratch");
     const int group = nq / nkv, chunks = (group + ROWS - 1) / ROWS;
     AttnArgs a{};
     a.q = q; a.kv = kv; a.out = out; a.block_table = block_table; a.bt_stride = bt_stride;
     a.seq_lens = seq_lens; a.splits = splits; a.nq = nq; a.nkv = nkv; a.d = d; a.page_size = page_size;
-    a.window = window; a.scale = scale; a.softcap = softcap; a.dv = d_out; a.v_in_k = dv < 0;
+    a.window = window; a.scale = scale; a.softcap = softcap; a.dv = d_one; a.v_in_k = dv < 0;
     a.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
+    if (apply_flags("attention_decode", a, flags)) return 1;
     a.part_o = scratch;
     a.part_ml = scratch ? scratch + (size_t)requests * nq * splits * d_out : nullptr;
     dim3 grid(requests, nkv * chunks, splits);
@@ -415,7 +443,7 @@ LILY_API int lily_attention_decode_simt(const void* q, const void* kv, void* out
     LILY_CHECK_LAUNCH("attention_decode");
     if (splits > 1) {
         dim3 cgrid(requests, nq), cblock(128, combine_staged(splits, d_out) ? COMBINE_ROWS : 1);
-        if (dtype == kBF16)
+        if (dtype == kBF16 && !a.out_f32)
             launch_pdl(attention_combine_kernel<__nv_bfloat16>, cgrid, cblock, 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (__nv_bfloat16*)out, nq, d_out, splits);
         else
             launch_pdl(attention_combine_kernel<float>, cgrid, cblock, 0, stream, (const float*)a.part_o, (const float*)a.part_ml, (float*)out, nq, d_out, splits);

@@ -30,7 +30,7 @@ from typing import List, Optional
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 SOURCES = ["elementwise.cu", "gemm_fp32.cu", "gemm_skinny.cu", "gemm_tcgen05.cu", "attention_simt.cu", "attention_mma.cu", "attention_tcgen05.cu", "sampling.cu",
-           "attention_decode_static.cu", "ssm.cu", "combine.cu", "wkv.cu", "latent.cu", "experts.cu", "latent_attention_mma.cu", "sublayer.cu", "diff_attention.cu"]
+           "attention_decode_static.cu", "ssm.cu", "combine.cu", "wkv.cu", "latent.cu", "experts.cu", "latent_attention_mma.cu", "sublayer.cu", "diff_attention.cu", "delta_rule.cu", "selective_scan.cu"]
 HEADERS = ["common.cuh", "attention_args.cuh", "no_alloc.h", "operand.cuh"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",

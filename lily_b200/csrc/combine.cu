@@ -3,6 +3,8 @@
 //   sigmoid gate:   out[t][c] *= sigmoid(gate[t][c])                    (an output gate ahead of a projection)
 //   normed mean:    out[t] = scale * sum_k rms(in_k[t]) * gain_k  (+ add[t])      as float32
 //
+//   head mix:       out[t][h][c] = sum_g mix[h][g] * in[t][g][kv(h)][c]                  (attention weights mixed over heads)
+//
 // where rms(v) = v / sqrt(mean(v^2) + eps).  Every input may be the activation dtype, float32, or the
 // float32 partial sums of a split-k product (added up in order while they are read); sums, roots and the
 // result are float32.
@@ -50,6 +52,26 @@ __global__ void sigmoid_gate_bf16x8_kernel(__nv_bfloat16* __restrict__ out, cons
             o2[k] = __floats2bfloat162_rn(__fdividef(o.x, 1.f + __expf(-g.x)), __fdividef(o.y, 1.f + __expf(-g.y)));
         }
         *reinterpret_cast<uint4*>(out + i) = ov;
+    }
+}
+
+// The heads' attention weights mixed by a matrix, applied behind the weighted sums: `in` holds, for every query head g,
+// its weights' sums over the values of every kv head, [tokens][nq][nkv][dv] in float32; head h takes the sums over its
+// own kv head's values from all query heads.  One block a token; the matrix [nq][nq] in shared memory.
+template <typename T>
+__global__ void head_mix_kernel(const float* __restrict__ in, const float* __restrict__ mix, T* __restrict__ out, int nq, int nkv, int dv) {
+    extern __shared__ float mix_s[];
+    pdl_enter_small();
+    for (int i = threadIdx.x; i < nq * nq; i += blockDim.x) mix_s[i] = mix[i];
+    __syncthreads();
+    const int group = nq / nkv;
+    const float* row = in + (size_t)blockIdx.x * nq * nkv * dv;
+    for (int e = threadIdx.x; e < nq * dv; e += blockDim.x) {
+        const int h = e / dv, c = e % dv;
+        const float* src = row + (size_t)(h / group) * dv + c;
+        float acc = 0.f;
+        for (int g = 0; g < nq; ++g) acc = fmaf(mix_s[h * nq + g], src[(size_t)g * nkv * dv], acc);
+        out[(size_t)blockIdx.x * nq * dv + e] = from_float<T>(acc);
     }
 }
 
@@ -185,6 +207,20 @@ LILY_API int lily_sigmoid_gate(void* out, int out_dtype, const void* gate, int g
     } else if (out_dtype == kBF16) launch_pdl(sigmoid_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)out, g, total);
     else launch_pdl(sigmoid_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)out, g, total);
     LILY_CHECK_LAUNCH("sigmoid_gate");
+    return 0;
+}
+
+LILY_API int lily_head_mix(const float* in, const float* mix, void* out, int tokens, int nq, int nkv, int dv, int out_dtype,
+                           cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    LILY_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0 && dv > 0, "head_mix: %d heads over %d kv heads of %d value columns", nq, nkv, dv);
+    const size_t smem = sizeof(float) * (size_t)nq * nq;
+    LILY_REQUIRE(smem <= 48 * 1024, "head_mix: a matrix over %d heads does not fit shared memory", nq);
+    int threads = (nq * dv + 31) / 32 * 32;
+    threads = threads > 256 ? 256 : threads;
+    if (out_dtype == kBF16) launch_pdl(head_mix_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), smem, stream, in, mix, (__nv_bfloat16*)out, nq, nkv, dv);
+    else launch_pdl(head_mix_kernel<float>, dim3(tokens), dim3(threads), smem, stream, in, mix, (float*)out, nq, nkv, dv);
+    LILY_CHECK_LAUNCH("head_mix");
     return 0;
 }
 

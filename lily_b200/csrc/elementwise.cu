@@ -282,16 +282,23 @@ __global__ void add_rmsnorm_multi_kernel(float* __restrict__ resid, const Summed
 
 __device__ __forceinline__ float silu_times(float g, float u) { return (g / (1.f + expf(-g))) * u; }
 
-// act(g) * u with act = SiLU (0) or the tanh form of GELU (1): 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))
-__device__ __forceinline__ float act_times(int act, float g, float u) {
+// act(g) * u with act = SiLU (0) or the tanh form of GELU (1): 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)));
+// act 2, the clamped form: g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit)
+__device__ __forceinline__ float act_times(int act, float g, float u, float limit = 0.f, float alpha = 1.f) {
     if (act == 0) return silu_times(g, u);
+    if (act == 2) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return (g / (1.f + expf(-alpha * g))) * (u + 1.f);
+    }
     return (0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)))) * u;
 }
 
 // The gate and up columns of one token alternate in runs of `block`: [gate block | up block | gate
 // block | ...]; block == inter is the plain [all gate | all up] order.
 template <typename T, typename IN, int VEC>
-__global__ void silu_mul_kernel(const Summed<IN> gate_up, T* __restrict__ out, int inter, int block, size_t total, int act) {
+__global__ void silu_mul_kernel(const Summed<IN> gate_up, T* __restrict__ out, int inter, int block, size_t total, int act,
+                                float limit, float alpha) {
     pdl_enter_small();
     const size_t step = (size_t)gridDim.x * blockDim.x * VEC;
     for (size_t idx = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC; idx < total; idx += step) {
@@ -300,9 +307,10 @@ __global__ void silu_mul_kernel(const Summed<IN> gate_up, T* __restrict__ out, i
         const size_t at = n * 2 * inter + (size_t)(i / block) * 2 * block + (i % block);
         if (VEC == 4) {
             const float4 g = gate_up.four(at), u = gate_up.four(at + block);
-            store4(out, idx, make_float4(act_times(act, g.x, u.x), act_times(act, g.y, u.y), act_times(act, g.z, u.z), act_times(act, g.w, u.w)));
+            store4(out, idx, make_float4(act_times(act, g.x, u.x, limit, alpha), act_times(act, g.y, u.y, limit, alpha),
+                                         act_times(act, g.z, u.z, limit, alpha), act_times(act, g.w, u.w, limit, alpha)));
         } else {
-            out[idx] = from_float<T>(act_times(act, gate_up(at), gate_up(at + block)));
+            out[idx] = from_float<T>(act_times(act, gate_up(at), gate_up(at + block), limit, alpha));
         }
     }
 }
@@ -347,7 +355,8 @@ __global__ void qk_norm_rope_write_kernel(const Summed<IN> qkv, const W* __restr
                                           const int* __restrict__ positions, const int* __restrict__ token_req,
                                           const int* __restrict__ block_table, int bt_stride,
                                           T* __restrict__ kv_layer, T* __restrict__ q_out,
-                                          int nq, int nkv, int dk, int rd, int page_size, int write_kv, int dv) {
+                                          int nq, int nkv, int dk, int rd, int page_size, int write_kv, int dv,
+                                          int v_norm, float v_blend, float* __restrict__ v_first, int v_first_mode) {
     pdl_enter_small();
     const int n = blockIdx.x;
     const int head = blockIdx.y * blockDim.y + threadIdx.y;
@@ -361,12 +370,14 @@ __global__ void qk_norm_rope_write_kernel(const Summed<IN> qkv, const W* __restr
     T* dst;
     const W* gain = nullptr;
     bool rotate = true;
+    int value_head = -1;
     if (head < nq) {
         dst = q_out + ((size_t)n * nq + head) * dk;
         gain = q_gain;
     } else {
         const int is_v = head >= nq + nkv;
         const int kvh = head - nq - (is_v ? nkv : 0);
+        if (is_v) value_head = kvh;
         const int page = block_table[(size_t)token_req[n] * bt_stride + pos / page_size];
         T* base = kv_layer + (size_t)page * nkv * page_size * (dk + dv);
         if (is_v) {
@@ -380,6 +391,26 @@ __global__ void qk_norm_rope_write_kernel(const Summed<IN> qkv, const W* __restr
         rotate = !is_v;
     }
     float inv = 1.f;
+    if (value_head >= 0 && (v_norm || v_first_mode)) {
+        // a value head brought to unit root mean square (no gain), then either kept for the layers that blend it into
+        // their own values (mode 1, float32, before it is rounded for the cache) or blended with the kept one (mode 2)
+        if (v_norm) {
+            float ssq = 0.f;
+            for (int i = lane; i < d; i += 32) {
+                const float x = qkv(src + i);
+                ssq += x * x;
+            }
+            inv = rsqrtf(warp_sum(ssq) / (float)d + eps);
+        }
+        float* kept = v_first ? v_first + ((size_t)n * nkv + value_head) * dv : nullptr;
+        for (int i = lane; i < d; i += 32) {
+            float x = qkv(src + i) * inv;
+            if (v_first_mode == 2) x = (1.f - v_blend) * x + v_blend * kept[i];
+            else if (v_first_mode == 1) kept[i] = x;
+            dst[i] = from_float<T>(x);
+        }
+        return;
+    }
     if (VEC == 2) {
         // two neighbouring features per lane and step (d, the rotary width and its half are even)
         if (gain) {
@@ -713,7 +744,7 @@ LILY_API int lily_add_rmsnorm_multi(float* resid, const void* delta_a, int a_dty
 }
 
 LILY_API int lily_silu_mul(const void* gate_up, void* out, int tokens, int inter, int block, int act_dtype,
-                           int in_dtype, int splits, size_t stride, int act, cudaStream_t stream) {
+                           int in_dtype, int splits, size_t stride, int act, float limit, float alpha, cudaStream_t stream) {
     const size_t total = (size_t)tokens * inter;
     if (total == 0) return 0;
     LILY_REQUIRE(block > 0 && inter % block == 0, "silu_mul: gate/up runs of %d do not tile %d columns", block, inter);
@@ -721,9 +752,10 @@ LILY_API int lily_silu_mul(const void* gate_up, void* out, int tokens, int inter
     const bool vec = block % 4 == 0 && stride % 4 == 0 && aligned16(gate_up) && aligned16(out);
     const size_t work = vec ? total / 4 : total;
     const int blocks = (int)((work + 255) / 256 < sm_count() * 16 ? (work + 255) / 256 : sm_count() * 16);
-#define GO(T, IN, V) launch_pdl(silu_mul_kernel<T, IN, V>, dim3(blocks), dim3(256), 0, stream, Summed<IN>{(const IN*)gate_up, splits, stride}, (T*)out, inter, block, total, act)
-    LILY_REQUIRE(act == 0 || act == 1, "silu_mul: activation %d (0: SiLU, 1: GELU, tanh form)", act);
-    if (act_dtype == kBF16 && in_dtype == kBF16 && splits == 1 && block % 8 == 0 && aligned16(gate_up) && aligned16(out)) {
+#define GO(T, IN, V) launch_pdl(silu_mul_kernel<T, IN, V>, dim3(blocks), dim3(256), 0, stream, Summed<IN>{(const IN*)gate_up, splits, stride}, (T*)out, inter, block, total, act, limit, alpha)
+    LILY_REQUIRE(act >= 0 && act <= 2, "silu_mul: activation %d (0: SiLU, 1: GELU, tanh form, 2: clamped)", act);
+    LILY_REQUIRE(act != 2 || limit > 0.f, "silu_mul: the clamped form needs a positive limit");
+    if (act != 2 && act_dtype == kBF16 && in_dtype == kBF16 && splits == 1 && block % 8 == 0 && aligned16(gate_up) && aligned16(out)) {
         const size_t work8 = total / 8;
         const int blocks8 = (int)((work8 + 255) / 256 < (size_t)sm_count() * 16 ? (work8 + 255) / 256 : (size_t)sm_count() * 16);
         launch_pdl(silu_mul_bf16x8_kernel, dim3(blocks8), dim3(256), 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, total, act);
@@ -740,9 +772,12 @@ LILY_API int lily_qk_norm_rope_write(const void* qkv, const void* q_gain, const 
                                      const int* token_req, const int* block_table, int bt_stride, void* kv_layer,
                                      void* q_out, int tokens, int nq, int nkv, int d, int rd, int page_size,
                                      int write_kv, int act_dtype, int gain_dtype, int in_dtype, int splits,
-                                     size_t stride, int dv, cudaStream_t stream) {
+                                     size_t stride, int dv, int v_norm, float v_blend, float* v_first, int v_first_mode,
+                                     cudaStream_t stream) {
     if (tokens == 0) return 0;
     if (dv <= 0) dv = d;
+    LILY_REQUIRE(v_first_mode >= 0 && v_first_mode <= 2 && (v_first_mode == 0) == (v_first == nullptr),
+                 "qk_norm_rope_write: kept values come with mode 1 (write) or 2 (blend)");
     LILY_REQUIRE(d > 0 && rd >= 0 && rd <= d && rd % 2 == 0, "qk_norm_rope_write: rotary_dim %d does not fit head_dim %d", rd, d);
     LILY_REQUIRE((q_gain == nullptr) == (k_gain == nullptr), "qk_norm_rope_write: q and k gains come together");
     LILY_REQUIRE((cos_t == nullptr) == (sin_t == nullptr), "qk_norm_rope_write: cos and sin tables come together");
@@ -755,11 +790,11 @@ LILY_API int lily_qk_norm_rope_write(const void* qkv, const void* q_gain, const 
 #define LAUNCH_V(T, W, IN, V)                                                                                     \
     launch_pdl(qk_norm_rope_write_kernel<T, W, IN, V>, grid, block, 0, stream, Summed<IN>{(const IN*)qkv, splits, stride}, \
         (const W*)q_gain, (const W*)k_gain, eps, cos_t, sin_t, positions, token_req, block_table, bt_stride,      \
-        (T*)kv_layer, (T*)q_out, nq, nkv, d, rot, page_size, write_kv, dv)
+        (T*)kv_layer, (T*)q_out, nq, nkv, d, rot, page_size, write_kv, dv, v_norm, v_blend, v_first, v_first_mode)
 #define LAUNCH(T, W, IN) do { if (vec) LAUNCH_V(T, W, IN, 2); else LAUNCH_V(T, W, IN, 1); } while (0)
     const bool gb = gain_dtype == kBF16, ib = in_dtype == kBF16;
     const int group = d / 16;
-    if (act_dtype == kBF16 && ib && splits == 1 && dv == d && d % 16 == 0 && group <= 32 && (group & (group - 1)) == 0 &&
+    if (!v_norm && !v_first_mode && act_dtype == kBF16 && ib && splits == 1 && dv == d && d % 16 == 0 && group <= 32 && (group & (group - 1)) == 0 &&
         (rot == d || rot == 0) && aligned16(qkv) && aligned16(kv_layer) && aligned16(q_out) && aligned16(q_gain) &&
         aligned16(k_gain) && aligned16(cos_t) && aligned16(sin_t)) {
         const int per_block = 128 / group;

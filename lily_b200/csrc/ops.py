@@ -27,16 +27,16 @@ _SIGNATURES = {
     "lily_logit_transform": [_vp, _sz, _f, _f, _vp],
     "lily_scatter_tokens": [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "lily_add_rmsnorm": [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _i, _i, _i, _sz, _vp],
-    "lily_silu_mul": [_vp, _vp, _i, _i, _i, _i, _i, _i, _sz, _i, _vp],
+    "lily_silu_mul": [_vp, _vp, _i, _i, _i, _i, _i, _i, _sz, _i, _f, _f, _vp],
     "lily_gemm_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     "lily_qk_norm_rope_write": [_vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i,
-                                _i, _i, _i, _i, _i, _sz, _i, _vp],
+                                _i, _i, _i, _i, _i, _sz, _i, _i, _f, _vp, _i, _vp],
     "lily_skinny_gemm": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "lily_skinny_swiglu": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "lily_cast": [_vp, _i, _vp, _i, _sz, _vp],
     "lily_gemm_fp32": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
-    "lily_attention_prefill_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _i, _vp],
-    "lily_attention_decode_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _i, _vp],
+    "lily_attention_prefill_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _i, _i, _vp],
+    "lily_attention_decode_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _i, _i, _vp],
     "lily_attention_combine": [_vp, _vp, _i, _i, _i, _i, _i, _vp],
     "lily_attention_prefill_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _i, _vp],
     "lily_attention_prefill_tc": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _f, _i, _vp],
@@ -47,7 +47,10 @@ _SIGNATURES = {
     "lily_normed_mean": [_vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _sz, _vp, _i, _i, _f, _f, _vp],
     "lily_causal_conv_silu": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _sz, _sz, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _vp],
     "lily_causal_conv": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _sz, _sz, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _vp],
-    "lily_add_normed_rmsnorm": [_vp, _vp, _i, _i, _sz, _vp, _f, _f, _vp, _i, _vp, _i, _vp, _i, _i, _f, _i, _vp],
+    "lily_add_normed_rmsnorm": [_vp, _vp, _i, _i, _sz, _vp, _f, _f, _vp, _i, _vp, _i, _vp, _i, _i, _f, _i, _i, _vp],
+    "lily_head_mix": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "lily_delta_rule": [_vp, _i, _i, _i, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _sz, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _f, _i, _vp],
+    "lily_selective_scan": [_vp, _vp, _i, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _vp, _sz, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
     "lily_activation": [_vp, _i, _i, _sz, _vp, _i, _sz, _i, _vp],
     "lily_diff_prepare": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp],
     "lily_diff_combine": [_vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _f, _f, _i, _vp],
@@ -122,6 +125,8 @@ def library():
         lib.lily_latent_attention_mma_tile_tokens.restype = _i
         lib.lily_latent_attention_status.restype = _i
         lib.lily_moe_tile_rows.restype = _i
+        lib.lily_delta_rule_max_head_dim.restype = _i
+        lib.lily_selective_scan_max_state.restype = _i
         _lib = lib
     return _lib
 
@@ -287,23 +292,26 @@ def add_rmsnorm_multi(resid: torch.Tensor, deltas: Sequence[torch.Tensor], gains
 
 
 ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+# the gate/up forms of the stand-alone kernel: the two above, and "swish_clamped": g' sigmoid(alpha g') (u' + 1) with
+# g' = min(g, limit) and u' = clamp(u, -limit, limit)
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "swish_clamped": 2}
 
 
 def silu_mul(gate_up: torch.Tensor, out_dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None,
-             block: Optional[int] = None, activation: str = "silu") -> torch.Tensor:
+             block: Optional[int] = None, activation: str = "silu", limit: float = 0.0, alpha: float = 1.0) -> torch.Tensor:
     """``act(gate) * up`` of ``gate_up`` [tokens, 2I] = [all gate | all up], or, with ``block``,
     alternating runs of ``block`` gate and ``block`` up columns; ``activation`` is "silu" or "gelu_tanh"
     (0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))).  ``gate_up`` may be float32 partial
     sums [splits, tokens, 2I], in which case ``out_dtype`` says what to write."""
-    if activation not in ACTIVATIONS:
-        raise KernelError(f"no gate activation {activation!r}; have {sorted(ACTIVATIONS)}")
+    if activation not in GATE_ACTIVATIONS:
+        raise KernelError(f"no gate activation {activation!r}; have {sorted(GATE_ACTIVATIONS)}")
     _dev(gate_up, out)
     n, two_i = gate_up.shape[-2:]
     splits, stride = _summed(gate_up, n, two_i, "silu_mul")
     if out is None:
         out = torch.empty((n, two_i // 2), dtype=out_dtype or gate_up.dtype, device=gate_up.device)
     _call("lily_silu_mul", _p(gate_up), _p(out), n, two_i // 2, int(block or two_i // 2), _dt(out), _dt(gate_up), splits,
-          stride, ACTIVATIONS[activation], _stream())
+          stride, GATE_ACTIVATIONS[activation], float(limit), float(alpha), _stream())
     return out
 
 
@@ -311,11 +319,15 @@ def qk_norm_rope_write(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain
                        eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
                        positions: torch.Tensor, token_req: torch.Tensor, block_table: torch.Tensor,
                        kv_layer: torch.Tensor, nq: int, nkv: int, d: int, rotary_dim: int, page_size: int,
-                       write_kv: bool = True, q_out: Optional[torch.Tensor] = None, dv: Optional[int] = None) -> torch.Tensor:
+                       write_kv: bool = True, q_out: Optional[torch.Tensor] = None, dv: Optional[int] = None,
+                       v_norm: bool = False, v_keep: Optional[torch.Tensor] = None, v_blend: Optional[float] = None) -> torch.Tensor:
     """Per-head RMSNorm of q and k (when gains are given), rotation by the tables, q to ``q_out``
     [tokens, nq * d], k and v into the token's place in its page of ``kv_layer``.  ``qkv`` is
     [tokens, (nq + nkv) d + nkv dv] in the cache's dtype or float32 partial sums [splits, tokens, ...]; value
-    heads have ``dv`` features (default d; see ``cache_layer_fits`` for the page layout)."""
+    heads have ``dv`` features (default d; see ``cache_layer_fits`` for the page layout).
+    ``v_norm``: each value head is divided by its root mean square (``eps``, no gain) before it is cached.
+    ``v_keep`` float32 [tokens, nkv * dv]: without ``v_blend`` the (normed) values are also left there; with it they
+    are read from there and the cached value is ``(1 - v_blend) v + v_blend v_keep``."""
     _dev(qkv, q_gain, k_gain, cos, sin, positions, token_req, block_table, kv_layer, q_out)
     n = qkv.shape[-2]
     dv = int(dv or d)
@@ -327,12 +339,18 @@ def qk_norm_rope_write(qkv: torch.Tensor, q_gain: Optional[torch.Tensor], k_gain
         raise KernelError("rotation tables must be float32 [positions, rotary_dim / 2]")
     if q_gain is not None and q_gain.dtype != k_gain.dtype:
         raise KernelError("q and k gains must share a dtype")
+    if v_keep is not None and (v_keep.dtype != torch.float32 or tuple(v_keep.shape) != (n, nkv * dv) or not v_keep.is_cuda
+                               or not v_keep.is_contiguous() or not write_kv):
+        raise KernelError("qk_norm_rope_write: kept values are float32 [tokens, nkv * dv] of a layer that writes its cache")
+    if v_blend is not None and v_keep is None:
+        raise KernelError("qk_norm_rope_write: a blend needs the kept values")
     if q_out is None:
         q_out = torch.empty((n, nq * d), dtype=kv_layer.dtype, device=qkv.device)
     _call("lily_qk_norm_rope_write", _p(qkv), _p(q_gain), _p(k_gain), float(eps), _p(cos), _p(sin),
           _i32(positions, "positions"), _i32(token_req, "token_req"), _i32(block_table, "block_table"),
           block_table.shape[-1], _p(kv_layer), _p(q_out), n, nq, nkv, d, rotary_dim, page_size, int(write_kv),
-          _dt(kv_layer), _dt(q_gain) if q_gain is not None else _F32, _dt(qkv), splits, stride, dv, _stream())
+          _dt(kv_layer), _dt(q_gain) if q_gain is not None else _F32, _dt(qkv), splits, stride, dv,
+          int(bool(v_norm)), float(v_blend or 0.0), _p(v_keep), 0 if v_keep is None else (1 if v_blend is None else 2), _stream())
     return q_out
 
 
@@ -565,13 +583,13 @@ def latent_attention_status() -> int:
 
 def prefill_tile_rows(dtype: torch.dtype = torch.float32, d: int = 0, page_size: int = 0, new_tokens: int = 0,
                       softcap: Optional[float] = None, dv: Optional[int] = None, values_in_keys: bool = False,
-                      heads: int = 0, keep_first: int = 0) -> int:
+                      heads: int = 0, keep_first: int = 0, sink: bool = False, all_values: bool = False) -> int:
     """New tokens per tile of the prefill kernel that will take this precision, head size (``dv`` for the values
     where it differs), page size, number of new tokens and kind of scores and mask."""
     lib = library()
     if values_in_keys and heads and latent_tensor_cores(dtype, d, dv, softcap=softcap):
         return int(lib.lily_latent_attention_mma_tile_tokens(int(heads)))
-    same = (dv is None or dv == d) and not values_in_keys
+    same = (dv is None or dv == d) and not values_in_keys and not sink and not all_values      # those run on CUDA cores
     if same and uses_tcgen05_attention(dtype, d, page_size, new_tokens):
         return int(lib.lily_attention_prefill_tc_rows())
     return int(lib.lily_attention_prefill_mma_rows() if same and uses_tensor_cores(dtype, d) else lib.lily_attention_prefill_simt_rows())
@@ -586,8 +604,12 @@ def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torc
                       prefix_lens: torch.Tensor, tile_req: torch.Tensor, tile_start: torch.Tensor, out: torch.Tensor,
                       nq: int, nkv: int, d: int, page_size: int, scale: float, window: Optional[int] = None,
                       tile_rows: Optional[int] = None, heads_per_block: int = 0, softcap: Optional[float] = None,
-                      dv: Optional[int] = None, values_in_keys: bool = False, keep_first: int = 0) -> None:
-    """Causal attention of each request's new tokens over its cached prefix and themselves.  ``softcap``: scores
+                      dv: Optional[int] = None, values_in_keys: bool = False, keep_first: int = 0,
+                      sink: bool = False, all_values: bool = False) -> None:
+    """Causal attention of each request's new tokens over its cached prefix and themselves.
+    ``sink``: the softmax's denominator holds one more unit (a key of score 0 that has no value).  ``all_values``: every
+    query head's weights meet the values of all kv heads, ``out`` is float32 [tokens, nq * nkv * dv] (``head_mix``
+    follows).  Both run on the CUDA-core kernel.  ``softcap``: scores
     become softcap * tanh(score * scale / softcap) before the softmax; ``keep_first``: beside a window, keys at
     positions below this stay visible; ``dv``: the
     value head size where it differs from d (CUDA-core kernels; ``out`` is then [tokens, nq * dv]).
@@ -597,8 +619,8 @@ def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torc
     kernel: the tcgen05 kernel takes tiles of its own size, the others theirs.  ``heads_per_block``
     (tcgen05 only) 1 or 2 picks between its one-head and its two-head form; 0 lets the launcher choose."""
     _dev(q, kv_layer, block_table, cu_seqlens, prefix_lens, tile_req, tile_start, out)
-    if q.dtype != kv_layer.dtype or out.dtype != q.dtype:
-        raise KernelError("attention: q, cache and out must share a dtype")
+    if q.dtype != kv_layer.dtype or out.dtype != (torch.float32 if all_values else q.dtype):
+        raise KernelError("attention: q, cache and out must share a dtype (sums over all kv heads' values are float32)")
     common = (_p(q), _p(kv_layer), _p(out), _i32(block_table, "block_table"), block_table.shape[-1],
               _i32(cu_seqlens, "cu_seqlens"), _i32(prefix_lens, "prefix_lens"), _i32(tile_req, "tile_req"),
               _i32(tile_start, "tile_start"), tile_req.numel(), nq, nkv, d, page_size, int(window or 0), float(scale))
@@ -613,10 +635,11 @@ def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torc
               page_size, int(window or 0), float(scale), _stream())
         return
     keep_first = int(keep_first or 0) if window else 0
-    tensor_cores = dv == d and not values_in_keys and uses_tensor_cores(q.dtype, d)
+    flags = _attention_flags(sink, all_values, values_in_keys, nkv, dv, out, q.shape[0] * nq)
+    tensor_cores = dv == d and not values_in_keys and not flags and uses_tensor_cores(q.dtype, d)
     base_rows = int(lib.lily_attention_prefill_mma_rows() if tensor_cores else lib.lily_attention_prefill_simt_rows())
     if tile_rows is not None and tile_rows != base_rows:
-        if not (tile_rows == int(lib.lily_attention_prefill_tc_rows()) and q.dtype == torch.bfloat16 and dv == d
+        if not (tile_rows == int(lib.lily_attention_prefill_tc_rows()) and q.dtype == torch.bfloat16 and dv == d and not flags
                 and lib.lily_attention_prefill_tc_takes(int(d), int(page_size))):
             raise KernelError(f"attention_prefill: no kernel with tiles of {tile_rows} rows for {q.dtype}, head size {d}, "
                               f"page size {page_size}")
@@ -626,7 +649,17 @@ def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torc
     elif tensor_cores:
         _call("lily_attention_prefill_mma", *common, cap, keep_first, _stream())
     else:
-        _call("lily_attention_prefill_simt", *common, _dt(q), cap, -dv if values_in_keys else dv, keep_first, _stream())
+        _call("lily_attention_prefill_simt", *common, _dt(q), cap, -dv if values_in_keys else dv, keep_first, flags, _stream())
+
+
+def _attention_flags(sink: bool, all_values: bool, values_in_keys: bool, nkv: int, dv: int, out: torch.Tensor, rows: int) -> int:
+    """The CUDA-core attention kernels' option bits: 1 the sink, 2 values of all kv heads, 4 float32 outputs."""
+    if all_values:
+        if values_in_keys:
+            raise KernelError("attention: values that are columns of the key rows belong to one shared head")
+        if out.dtype != torch.float32 or out.numel() != rows * nkv * dv:
+            raise KernelError(f"attention: sums over all kv heads' values are float32 [rows, nq * {nkv} * {dv}]")
+    return (1 if sink else 0) | (6 if all_values else 0)
 
 
 def decode_clusters(d: int, splits: int, group: int) -> int:
@@ -643,17 +676,19 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
                      out: torch.Tensor, scratch: Optional[torch.Tensor], splits: int, nq: int, nkv: int, d: int,
                      page_size: int, scale: float, window: Optional[int] = None, stages: int = 0,
                      softcap: Optional[float] = None, dv: Optional[int] = None, values_in_keys: bool = False,
-                     keep_first: int = 0) -> None:
-    """One query token per request (rows of ``q`` [requests, nq * d]) over ``seq_lens`` cached
+                     keep_first: int = 0, sink: bool = False, all_values: bool = False) -> None:
+    """``sink`` and ``all_values`` as in ``attention_prefill`` (CUDA-core kernel; the scratch then holds nkv * dv columns a head).
+    One query token per request (rows of ``q`` [requests, nq * d]) over ``seq_lens`` cached
     positions (the last ``window`` of them and the first ``keep_first``, where given), keys cut into ``splits`` ranges merged through ``scratch`` (float32).  ``stages`` (tensor-core
     kernel only): the key/value tiles a block holds, 0 for the default (``DecodePlan.stages``)."""
     _dev(q, kv_layer, block_table, seq_lens, out, scratch)
     requests = q.shape[0]
-    if q.dtype != kv_layer.dtype or out.dtype != q.dtype:
-        raise KernelError("attention: q, cache and out must share a dtype")
+    if q.dtype != kv_layer.dtype or out.dtype != (torch.float32 if all_values else q.dtype):
+        raise KernelError("attention: q, cache and out must share a dtype (sums over all kv heads' values are float32)")
     dv = int(dv or d)
     cap = float(softcap or 0.0)
-    need = decode_scratch_floats(requests, nq, dv, splits)
+    flags = _attention_flags(sink, all_values, values_in_keys, nkv, dv, out, requests * nq)
+    need = decode_scratch_floats(requests, nq, nkv * dv if all_values else dv, splits)
     if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
         raise KernelError(f"attention_decode: scratch of {need} float32 needed")
     common = (_p(q), _p(kv_layer), _p(out), _i32(block_table, "block_table"), block_table.shape[-1],
@@ -665,7 +700,7 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
               int(window or 0), float(scale), _stream())
         if splits > 1:
             _call("lily_attention_combine", _p(scratch), _p(out), requests, nq, dv, splits, _dt(q), _stream())
-    elif dv == d and not values_in_keys and uses_tensor_cores(q.dtype, d):
+    elif dv == d and not values_in_keys and not flags and uses_tensor_cores(q.dtype, d):
         _call("lily_attention_decode_mma", *common, int(stages), cap, int(keep_first or 0) if window else 0, _stream())   # merges the splits itself (cluster, or combine behind)
         if splits > 1 and (stages or requests * nkv * -(-(nq // nkv) // 16) > decode_clusters(d, splits, nq // nkv)):
             launches["count"] += 1                                   # the combine kernel, launched inside
@@ -673,7 +708,7 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
         if stages:
             raise KernelError(f"attention_decode: {stages} stages are the tensor-core kernel's; {q.dtype}, head size {d} runs on CUDA cores")
         _call("lily_attention_decode_simt", *common, _dt(q), cap, -dv if values_in_keys else dv,
-              int(keep_first or 0) if window else 0, _stream())
+              int(keep_first or 0) if window else 0, flags, _stream())
         if splits > 1:
             launches["count"] += 1          # the combine kernel, launched inside
 
@@ -754,12 +789,14 @@ def whole_rows_pay(pairs: int, sm_count: int = 148) -> bool:
 
 def plan_decode_attention(dtype: torch.dtype, requests: int, nq: int, nkv: int, d: int, max_seq_len: int,
                           even: bool = False, dv: Optional[int] = None, values_in_keys: bool = False,
-                          keep_first: int = 0, fusable: bool = True) -> DecodePlan:
+                          keep_first: int = 0, fusable: bool = True, cuda_cores: bool = False) -> DecodePlan:
     """The plan for ``requests`` rows that bring one token each, none longer than ``max_seq_len`` positions.
     A step in which every request brings one token may hand the qkv product straight to the attention kernel
     (``fused``): every block then finishes its own queries, which costs less than a kernel of its own while all
     blocks are resident at once (three a SM) and more when they run in several rounds (measured at batch 64:
     2 % of the step).
+    ``cuda_cores``: the attention has options only the CUDA-core kernel has (a sink, values of all kv heads; ``dv`` is
+    then the width of a head's output row).
     ``fusable`` False: the caller prepares queries and cache itself (something stands between its projection and
     the attention); ``keep_first``: the window keeps the first positions in sight (the caller then prepares queries
     and cache itself as well).
@@ -771,7 +808,7 @@ def plan_decode_attention(dtype: torch.dtype, requests: int, nq: int, nkv: int, 
         return DecodePlan(1, False, 0, "single")
     group = nq // nkv
     dv = int(dv or d)
-    tensor_cores = dv == d and not values_in_keys and uses_tensor_cores(dtype, d)      # values of another head size run on CUDA cores
+    tensor_cores = dv == d and not values_in_keys and not cuda_cores and uses_tensor_cores(dtype, d)      # values of another head size run on CUDA cores
     fusable = fusable and not keep_first          # the kernel that takes the projection itself has no kept first positions
     row_blocks = -(-group // 16)                 # the tensor-core kernel takes 16 query heads of a kv head a block
     pairs = requests * nkv * row_blocks
@@ -1443,8 +1480,10 @@ _FUSED_ACTIVATION = os.environ.get("LILY_B200_FUSED_ACTIVATION", "1") != "0"
 
 def add_normed_rmsnorm(resid: torch.Tensor, delta: torch.Tensor, post_gain: torch.Tensor, post_eps: float, mult: float,
                        weight: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype,
-                       rows: Optional[torch.Tensor] = None, write_residual: bool = True) -> Optional[torch.Tensor]:
-    """``resid += mult * (delta / rms(delta) * post_gain)`` in float32 (``delta`` [tokens, width] in either dtype, or
+                       rows: Optional[torch.Tensor] = None, write_residual: bool = True,
+                       normalise: bool = True) -> Optional[torch.Tensor]:
+    """``normalise`` False: ``resid += mult * (delta * post_gain)``, a gain per column without the division.
+    ``resid += mult * (delta / rms(delta) * post_gain)`` in float32 (``delta`` [tokens, width] in either dtype, or
     float32 partial sums [splits, tokens, width]), then the new rows divided by their root mean square times ``weight``
     in ``out_dtype`` (None without ``weight``: the add alone).  With ``rows`` only those tokens' outputs are formed and
     the stream is left as it is."""
@@ -1465,7 +1504,7 @@ def add_normed_rmsnorm(resid: torch.Tensor, delta: torch.Tensor, post_gain: torc
         return None
     _call("lily_add_normed_rmsnorm", _p(resid), ptr, dt, splits, stride, _p(post_gain), float(post_eps), float(mult),
           _p(weight), _dt(weight) if weight is not None else _F32, _p(out), _dt(out) if out is not None else _F32,
-          _i32(rows, "rows"), n_out, width, float(eps), int(bool(write_residual)), _stream())
+          _i32(rows, "rows"), n_out, width, float(eps), int(bool(write_residual)), int(bool(normalise)), _stream())
     return out
 
 
@@ -1527,4 +1566,73 @@ def diff_combine(maps_out: torch.Tensor, proj: torch.Tensor, gate_col: int, head
     out = torch.empty((n, heads * dv), dtype=maps_out.dtype, device=maps_out.device)
     _call("lily_diff_combine", _p(maps_out), _p(proj), proj.shape[1], int(gate_col), _p(out), n, heads, dv, maps,
           float(lam), float(out_scale), float(eps), _dt(maps_out), _stream())
+    return out
+
+
+# ------------------------------------------------------------------------------ mixed heads, delta rule, selective scan
+
+def head_mix(sums: torch.Tensor, mix: torch.Tensor, nq: int, nkv: int, dv: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """``out[t, h] = sum_g mix[h, g] * sums[t, g, kv(h)]``: ``sums`` float32 [tokens, nq * nkv * dv] holds every query
+    head's attention weights summed over the values of every kv head (``attention_*`` with ``all_values``), ``mix``
+    float32 [nq, nq]; returns [tokens, nq * dv], each head over its own kv head's values with the mixed weights."""
+    _dev(sums, mix)
+    tokens = sums.shape[0]
+    if sums.dtype != torch.float32 or mix.dtype != torch.float32 or sums.shape[1] != nq * nkv * dv or tuple(mix.shape) != (nq, nq):
+        raise KernelError("head_mix: float32 sums [tokens, nq * nkv * dv] and a float32 matrix [nq, nq]")
+    out = torch.empty((tokens, nq * dv), dtype=out_dtype, device=sums.device)
+    _call("lily_head_mix", _p(sums), _p(mix), _p(out), tokens, nq, nkv, dv, _dt(out), _stream())
+    return out
+
+
+def delta_rule_max_head_dim() -> int:
+    return int(library().lily_delta_rule_max_head_dim())
+
+
+def delta_rule(qkv: torch.Tensor, proj: torch.Tensor, b_col: int, a_col: int, a_log: torch.Tensor, dt_bias: torch.Tensor,
+               state: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor, requests: int, heads: int, kv_heads: int,
+               d: int, dv: int, unit_eps: float, q_scale: float) -> torch.Tensor:
+    """The gated delta rule over each request's new tokens, from and to ``state[slot, :heads * dv * d]`` (float32,
+    a head's matrix as [dv, d]).  ``qkv`` [tokens, (2 kv_heads) d + heads dv]: q, k, v behind their convolution and
+    activation; ``proj`` [tokens, width]: ``heads`` columns from ``b_col`` (the write strength before its sigmoid) and
+    from ``a_col`` (the decay's input).  q and k are made unit vectors per head here (``unit_eps`` inside the root; q
+    times ``q_scale``); the decay is ``exp(-exp(a_log) softplus(a + dt_bias))``.  Returns float32 [tokens, heads * dv],
+    each token read out after its own write."""
+    _dev(qkv, proj, a_log, dt_bias, state, cu_seqlens, slots)
+    n = qkv.shape[0]
+    if qkv.shape[1] != 2 * kv_heads * d + heads * dv or proj.shape[0] != n or qkv.dtype != proj.dtype:
+        raise KernelError("delta_rule: qkv is [tokens, 2 kv_heads d + heads dv] in the projection's dtype")
+    if max(b_col, a_col) + heads > proj.shape[1] or a_log.dtype != torch.float32 or dt_bias.dtype != torch.float32 \
+            or a_log.numel() != heads or dt_bias.numel() != heads or state.dtype != torch.float32 or state.dim() != 2:
+        raise KernelError("delta_rule: columns out of range, or decay constants / state not float32")
+    y = torch.empty((n, heads * dv), dtype=torch.float32, device=qkv.device)
+    _call("lily_delta_rule", _p(qkv), qkv.shape[1], 0, kv_heads * d, 2 * kv_heads * d, _p(proj), proj.shape[1], int(b_col),
+          int(a_col), _p(a_log), _p(dt_bias), _p(state), state.shape[1], _p(y), _i32(cu_seqlens, "cu_seqlens"),
+          _i32(slots, "slots"), int(requests), heads, kv_heads, d, dv, float(unit_eps), float(q_scale), _dt(qkv), _stream())
+    return y
+
+
+def selective_scan_max_state() -> int:
+    return int(library().lily_selective_scan_max_state())
+
+
+def selective_scan(x: torch.Tensor, low: torch.Tensor, b_col: int, step: torch.Tensor, proj: torch.Tensor, z_col: int,
+                   a: torch.Tensor, d_skip: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor,
+                   requests: int) -> torch.Tensor:
+    """The selective scan with a state vector per channel over each request's new tokens, from and to
+    ``state[slot, :inner * n]`` (float32).  ``x`` [tokens, inner]: the convolved, activated inputs; ``low``
+    [tokens, width]: B in the ``n`` columns from ``b_col``, C in the ``n`` after them; ``step`` float32 [tokens, inner]:
+    the step projection with its bias, before softplus; the gate z in ``proj[:, z_col:z_col + inner]``; ``a`` float32
+    [inner, n] (negative); ``d_skip`` float32 [inner].  Returns ``(S . C + D x) * silu(z)`` in ``x``'s dtype."""
+    _dev(x, low, step, proj, a, d_skip, state, cu_seqlens, slots)
+    tokens, inner = x.shape
+    n = a.shape[1]
+    if step.dtype != torch.float32 or tuple(step.shape) != (tokens, inner) or a.dtype != torch.float32 or a.shape[0] != inner \
+            or d_skip.dtype != torch.float32 or d_skip.numel() != inner or state.dtype != torch.float32 or state.dim() != 2:
+        raise KernelError("selective_scan: float32 steps [tokens, inner], A [inner, n], D [inner] and state")
+    if low.dtype != x.dtype or proj.dtype != x.dtype or b_col + 2 * n > low.shape[1] or z_col + inner > proj.shape[1]:
+        raise KernelError("selective_scan: B, C or gate columns out of range, or dtypes differ")
+    out = torch.empty((tokens, inner), dtype=x.dtype, device=x.device)
+    _call("lily_selective_scan", _p(x), _p(low), low.shape[1], int(b_col), int(b_col) + n, _p(step), _p(proj), proj.shape[1],
+          int(z_col), _p(a), _p(d_skip), _p(state), state.shape[1], _p(out), _i32(cu_seqlens, "cu_seqlens"),
+          _i32(slots, "slots"), int(requests), inner, n, _dt(x), _stream())
     return out

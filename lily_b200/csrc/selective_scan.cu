@@ -1,0 +1,151 @@
+// The selective scan of the first Mamba mixer: a state vector per channel, with its state in the request's slot.
+//
+// Per channel c and state entry n, with dt_t[c] = softplus(step_t[c]) (the step projection's result with its bias) and
+// A[c][n] = -exp(A_log[c][n]) formed once when the weights are loaded:
+//
+//     S[c][n] <- exp(dt_t[c] A[c][n]) S[c][n] + dt_t[c] x_t[c] B_t[n]
+//     y_t[c]  =  sum_n S[c][n] C_t[n] + D[c] x_t[c],        out_t[c] = y_t[c] * silu(z_t[c])
+//
+// SL lanes share a channel and hold NR state entries each; a block owns SCAN_CHANNELS channels of one request and
+// walks the request's new tokens in order; a token's B and C are staged once for all of the block's channels.  The
+// step size, the decay, the state and the sums are float32 whatever the activation dtype.  State row of a slot:
+// [inner][state] (state fastest) at the row's start.
+#include "common.cuh"
+
+namespace lily {
+
+constexpr int SL = 8;                   // lanes that share a channel
+constexpr int SCAN_TOKENS = 16;         // tokens staged at a time
+constexpr int SCAN_THREADS = 128;
+constexpr int SCAN_CHANNELS = SCAN_THREADS / SL;
+
+struct SelectiveArgs {
+    const void* x;            // [tokens, inner]: the convolved and activated inputs
+    const void* low;          // [tokens, low_stride]: B at b_col, C at c_col (n_state columns each)
+    int low_stride, b_col, c_col;
+    const float* step;        // [tokens, inner]: W_dt . + bias, before softplus
+    const void* z;            // [tokens, z_stride]: the gate's columns start at z_col
+    int z_stride, z_col;
+    const float* A;           // [inner, n_state]
+    const float* D;           // [inner]
+    float* state;             // [slots, state_stride]
+    size_t state_stride;
+    void* out;                // [tokens, inner]
+    const int* cu_seqlens;
+    const int* slots;
+    int inner, n_state;
+};
+
+// grid (requests, ceil(inner / SCAN_CHANNELS)), block SCAN_THREADS; n_state <= SL * NR
+template <typename T, int NR>
+__global__ void __launch_bounds__(SCAN_THREADS) selective_scan_kernel(const SelectiveArgs a) {
+    constexpr int SP = SL * NR;
+    __shared__ float Bs[SCAN_TOKENS][SP], Cs[SCAN_TOKENS][SP];
+    __shared__ float dts[SCAN_TOKENS][SCAN_CHANNELS], xs[SCAN_TOKENS][SCAN_CHANNELS], zs[SCAN_TOKENS][SCAN_CHANNELS],
+        ys[SCAN_TOKENS][SCAN_CHANNELS];
+    pdl_enter_small();
+    const int req = blockIdx.x, ch0 = blockIdx.y * SCAN_CHANNELS;
+    const int l = threadIdx.x % SL, cg = threadIdx.x / SL;
+    const int ch = ch0 + cg, inner = a.inner, ns = a.n_state;
+    const bool ch_ok = ch < inner;
+    const int tok0 = a.cu_seqlens[req], len = a.cu_seqlens[req + 1] - tok0;
+    if (len <= 0) return;
+    float* st = a.state + (size_t)a.slots[req] * a.state_stride + (size_t)(ch_ok ? ch : 0) * ns;
+    float S[NR], A[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        const int n = l + SL * r;
+        const bool ok = ch_ok && n < ns;
+        S[r] = ok ? st[n] : 0.f;
+        A[r] = ok ? a.A[(size_t)ch * ns + n] : 0.f;
+    }
+    const float skip = ch_ok ? a.D[ch] : 0.f;
+    const T* x = (const T*)a.x;
+    const T* low = (const T*)a.low;
+    const T* z = (const T*)a.z;
+    T* out = (T*)a.out;
+
+    for (int t0 = 0; t0 < len; t0 += SCAN_TOKENS) {
+        const int n = min(SCAN_TOKENS, len - t0);
+        __syncthreads();
+        for (int e = threadIdx.x; e < n * SP; e += SCAN_THREADS) {
+            const int t = e / SP, i = e % SP;
+            const T* row = low + (size_t)(tok0 + t0 + t) * a.low_stride + i;
+            Bs[t][i] = i < ns ? to_float(row[a.b_col]) : 0.f;
+            Cs[t][i] = i < ns ? to_float(row[a.c_col]) : 0.f;
+        }
+        for (int e = threadIdx.x; e < n * SCAN_CHANNELS; e += SCAN_THREADS) {
+            const int t = e / SCAN_CHANNELS, c = e % SCAN_CHANNELS;
+            const size_t tok = tok0 + t0 + t;
+            const bool ok = ch0 + c < inner;
+            const float s = ok ? a.step[tok * inner + ch0 + c] : 0.f;
+            dts[t][c] = s > 20.f ? s : log1pf(expf(s));
+            xs[t][c] = ok ? to_float(x[tok * inner + ch0 + c]) : 0.f;
+            zs[t][c] = ok ? to_float(z[tok * a.z_stride + a.z_col + ch0 + c]) : 0.f;
+        }
+        __syncthreads();
+        for (int t = 0; t < n; ++t) {
+            const float dt = dts[t][cg], xv = xs[t][cg], dx = dt * xv;
+            float acc = 0.f;
+#pragma unroll
+            for (int r = 0; r < NR; ++r) {
+                S[r] = fmaf(expf(dt * A[r]), S[r], dx * Bs[t][l + SL * r]);
+                acc = fmaf(S[r], Cs[t][l + SL * r], acc);
+            }
+#pragma unroll
+            for (int o = SL / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            if (l == 0) {
+                const float zv = zs[t][cg];
+                ys[t][cg] = fmaf(skip, xv, acc) * (zv / (1.f + expf(-zv)));
+            }
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < n * SCAN_CHANNELS; e += SCAN_THREADS) {
+            const int t = e / SCAN_CHANNELS, c = e % SCAN_CHANNELS;
+            if (ch0 + c < inner) out[(size_t)(tok0 + t0 + t) * inner + ch0 + c] = from_float<T>(ys[t][c]);
+        }
+    }
+    if (ch_ok) {
+#pragma unroll
+        for (int r = 0; r < NR; ++r) {
+            const int n = l + SL * r;
+            if (n < ns) st[n] = S[r];
+        }
+    }
+}
+
+}  // namespace lily
+
+using namespace lily;
+
+LILY_API int lily_selective_scan_max_state() { return SL * 32; }
+
+LILY_API int lily_selective_scan(const void* x, const void* low, int low_stride, int b_col, int c_col, const float* step,
+                                 const void* z, int z_stride, int z_col, const float* A, const float* D, float* state,
+                                 size_t state_stride, void* out, const int* cu_seqlens, const int* slots, int requests,
+                                 int inner, int n_state, int dtype, cudaStream_t stream) {
+    if (requests == 0) return 0;
+    LILY_REQUIRE(inner > 0 && n_state > 0 && n_state <= SL * 32, "selective_scan: %d channels of %d state entries (up to %d)", inner, n_state, SL * 32);
+    LILY_REQUIRE((size_t)inner * n_state <= state_stride, "selective_scan: the state row is shorter than %d x %d", inner, n_state);
+    LILY_REQUIRE((inner + SCAN_CHANNELS - 1) / SCAN_CHANNELS <= 65535, "selective_scan: %d channels", inner);
+    SelectiveArgs a{};
+    a.x = x; a.low = low; a.low_stride = low_stride; a.b_col = b_col; a.c_col = c_col; a.step = step;
+    a.z = z; a.z_stride = z_stride; a.z_col = z_col; a.A = A; a.D = D; a.state = state; a.state_stride = state_stride;
+    a.out = out; a.cu_seqlens = cu_seqlens; a.slots = slots; a.inner = inner; a.n_state = n_state;
+    dim3 grid(requests, (inner + SCAN_CHANNELS - 1) / SCAN_CHANNELS), block(SCAN_THREADS);
+    const int per = (n_state + SL - 1) / SL;
+#define GO(NR)                                                                                                 \
+    do {                                                                                                       \
+        if (dtype == kBF16) launch_pdl(selective_scan_kernel<__nv_bfloat16, NR>, grid, block, 0, stream, a);   \
+        else launch_pdl(selective_scan_kernel<float, NR>, grid, block, 0, stream, a);                          \
+    } while (0)
+    if (per <= 1) GO(1);
+    else if (per <= 2) GO(2);
+    else if (per <= 4) GO(4);
+    else if (per <= 8) GO(8);
+    else if (per <= 16) GO(16);
+    else GO(32);
+#undef GO
+    LILY_CHECK_LAUNCH("selective_scan");
+    return 0;
+}

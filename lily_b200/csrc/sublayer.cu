@@ -1,6 +1,8 @@
 // Kernels around a sublayer that has a norm behind it as well as ahead of it, and the plain (ungated) feed-forward.
 //
-//   add_normed_rmsnorm:  u = delta / sqrt(mean(delta^2) + eps_post) * gain_post         (the norm behind the sublayer)
+//   add_normed_rmsnorm:  u = delta / sqrt(mean(delta^2) + eps_post) * gain_post         (the norm behind the sublayer; or, with
+//                                                                                         `normalise` 0, u = delta * gain_post: a gain
+//                                                                                         per column alone, a layer scale)
 //                        v = resid + mult * u;  resid = v (when asked)                   (the add, float32)
 //                        out = v / sqrt(mean(v^2) + eps) * weight                        (the norm ahead of the next one)
 //   activation:          out = act(in), act = SiLU, the tanh form of GELU, or the square of max(., 0)
@@ -27,6 +29,7 @@ struct NormedAddArgs {
     int hidden;
     float post_eps, eps, mult;
     int write_residual;
+    int normalise;            // 0: the delta is not divided by its root mean square (post_gain alone scales it)
 };
 
 __device__ __forceinline__ float gain_at(const void* w, int bf16, int i) {
@@ -56,7 +59,8 @@ __global__ void add_normed_rmsnorm_kernel(const NormedAddArgs a) {
             ssq = fmaf(d, d, ssq);
         }
     }
-    const float inv_d = rsqrtf(block_sum(ssq, red) / (float)hidden + a.post_eps);
+    const float inv_d = a.normalise ? rsqrtf(block_sum(ssq, red) / (float)hidden + a.post_eps) : 1.f;
+    __syncthreads();               // the row is whole before other threads' entries are read (the sum above may be skipped)
     ssq = 0.f;
     if (VEC == 4) {
         for (int i = threadIdx.x * 4; i < hidden; i += blockDim.x * 4) {
@@ -124,7 +128,7 @@ __global__ void add_normed_rmsnorm_reg_kernel(const NormedAddArgs a) {
         v[k] = *reinterpret_cast<const float4*>(a.resid + src + i);
         ssq += d[k].x * d[k].x + d[k].y * d[k].y + d[k].z * d[k].z + d[k].w * d[k].w;
     }
-    const float inv_d = rsqrtf(block_sum_once(ssq, slots[0]) / (float)hidden + a.post_eps);
+    const float inv_d = a.normalise ? rsqrtf(block_sum_once(ssq, slots[0]) / (float)hidden + a.post_eps) : 1.f;
     ssq = 0.f;
 #pragma unroll
     for (int k = 0; k < PER; ++k) {
@@ -163,13 +167,15 @@ __global__ void add_normed_rmsnorm_cluster_kernel(const NormedAddArgs a) {
     const float4 d = a.delta.four(src + i);
     const float4 g = *reinterpret_cast<const float4*>(a.post_gain + i);
     float4 v = *reinterpret_cast<const float4*>(a.resid + src + i);
-    float mine = block_sum(d.x * d.x + d.y * d.y + d.z * d.z + d.w * d.w, red);
-    if (threadIdx.x < CL) cluster.map_shared_rank(&share[0][0], threadIdx.x)[blockIdx.x] = mine;
-    cluster.sync();
-    float total = 0.f;
+    float mine = 0.f, total = 0.f, inv_d = 1.f;
+    if (a.normalise) {                                                  // the same branch in every block of the launch
+        mine = block_sum(d.x * d.x + d.y * d.y + d.z * d.z + d.w * d.w, red);
+        if (threadIdx.x < CL) cluster.map_shared_rank(&share[0][0], threadIdx.x)[blockIdx.x] = mine;
+        cluster.sync();
 #pragma unroll
-    for (int r = 0; r < CL; ++r) total += share[0][r];                  // same order in every block
-    const float inv_d = rsqrtf(total / (float)hidden + a.post_eps);
+        for (int r = 0; r < CL; ++r) total += share[0][r];              // same order in every block
+        inv_d = rsqrtf(total / (float)hidden + a.post_eps);
+    }
     v.x += a.mult * ((d.x * inv_d) * g.x);
     v.y += a.mult * ((d.y * inv_d) * g.y);
     v.z += a.mult * ((d.z * inv_d) * g.z);
@@ -237,7 +243,7 @@ using namespace lily;
 LILY_API int lily_add_normed_rmsnorm(float* resid, const void* delta, int delta_dtype, int delta_splits, size_t delta_stride,
                                      const float* post_gain, float post_eps, float mult, const void* weight, int weight_dtype,
                                      void* out, int out_dtype, const int* rows, int n_out, int hidden, float eps,
-                                     int write_residual, cudaStream_t stream) {
+                                     int write_residual, int normalise, cudaStream_t stream) {
     if (n_out == 0) return 0;
     LILY_REQUIRE(delta_splits >= 1 && (delta_splits == 1 || delta_dtype == kF32), "add_normed_rmsnorm: only float32 partial sums come in several splits");
     LILY_REQUIRE(hidden > 0 && hidden <= 48 * 1024, "add_normed_rmsnorm: width %d", hidden);
@@ -246,7 +252,7 @@ LILY_API int lily_add_normed_rmsnorm(float* resid, const void* delta, int delta_
     NormedAddArgs a{};
     a.resid = resid; a.delta = Operand{delta, delta_dtype == kBF16, delta_splits, delta_stride}; a.post_gain = post_gain;
     a.weight = weight; a.weight_bf16 = weight_dtype == kBF16; a.out = out; a.rows = rows; a.hidden = hidden;
-    a.post_eps = post_eps; a.eps = eps; a.mult = mult; a.write_residual = write_residual;
+    a.post_eps = post_eps; a.eps = eps; a.mult = mult; a.write_residual = write_residual; a.normalise = normalise;
     const bool vec = hidden % 4 == 0 && a.delta.vector_ok() && ((uintptr_t)resid & 15) == 0 && ((uintptr_t)post_gain & 15) == 0;
     constexpr int CL = 8;
     if (vec && n_out <= 64 && hidden % (4 * CL * 32) == 0 && hidden / (4 * CL) <= 1024) {

@@ -1,3 +1,3 @@
 """Architectures this package ships; importing the package registers them."""
 
-from lily_b200.models import dense_decoder, godotar, gotivik, zirurax  # noqa: F401
+from lily_b200.models import dense_decoder, godotar, gotivik, kinanex, zirurax  # noqa: F401

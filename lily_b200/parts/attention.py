@@ -50,13 +50,28 @@ class AttentionSpec:
     names: Optional[Tuple[Tuple[str, str], ...]] = None
     keep_first: int = 0                   # with a window: key j is also seen when j < keep_first
     conv_taps: int = 0                    # 0: none; n: y_t = sum_j w[:, j] u_(t - n + 1 + j) on each channel of q, k and v
+    out_bias: bool = True                 # with ``bias``: the output projection has one too
+    sink: bool = False                    # weights exp(s_j) / (1 + sum exp(s_j)): a key of score 0 that has no value
+    talk: bool = False                    # weights_h <- sum_g T[h, g] weights_g with T the tensor of role "talk" [heads, heads]
+    v_norm: bool = False                  # each value head divided by its root mean square (norm_eps, no gain), cached so
+    # "first": this layer's (normed) values are kept for the step; "blend": the cached value is
+    # (1 - lambda) v + lambda v_first with lambda the scalar tensor of role "v_blend" and v_first the kept values of
+    # the same token; layers that share have one kv_heads x v_head_dim
+    v_share: Optional[str] = None
 
     @property
     def value_dim(self) -> int:
         return self.v_head_dim or self.head_dim
 
     def name(self, role: str) -> str:
-        default = f"{role[0]}_proj.conv" if role.endswith("_conv") else f"{role}_proj.weight"
+        if role.endswith("_conv"):
+            default = f"{role[0]}_proj.conv"
+        elif role.endswith("_bias"):
+            default = f"{role[0]}_proj.bias"
+        elif role.endswith("_norm"):
+            default = f"{role[0]}_norm.weight"
+        else:
+            default = f"{role}_proj.weight" if role in ("q", "k", "v", "o", "g") else role
         return dict(self.names or ()).get(role, default)
 
     @property
@@ -95,8 +110,12 @@ class Attention(Mixer):
         self.scale = spec.scale if spec.scale is not None else spec.head_dim ** -0.5
         self.position = build_part("position", spec.position, prefix, ctx) if spec.position is not None else None
         self.w_qkv = self.b_qkv = self.w_o = self.b_o = self.q_gain = self.k_gain = self.w_g = None
-        if spec.value_dim != spec.head_dim and (spec.bias or spec.qk_norm):
-            raise ValueError("a value head size of its own comes without biases and q/k norms")
+        if spec.v_share not in (None, "first", "blend"):
+            raise ValueError(f"values are shared as 'first' or 'blend', not {spec.v_share!r}")
+        if (spec.sink or spec.talk or spec.v_norm or spec.v_share) and (spec.conv_taps or spec.softcap or spec.window or spec.out_gate):
+            raise ValueError("sink, mixed heads and normed or shared values come without convolution, cap, window and gate")
+        self.talk = None
+        self.v_blend = None
         if spec.keep_first and not spec.window:
             raise ValueError("first positions are kept in sight only beside a window")
         if spec.conv_taps < 0 or (spec.conv_taps and spec.bias):
@@ -131,13 +150,18 @@ class Attention(Mixer):
                         f"{p}.{s.name('k_conv')}": TensorSpec((kv, s.conv_taps), role="vector", init="normal"),
                         f"{p}.{s.name('v_conv')}": TensorSpec((s.num_kv_heads * s.value_dim, s.conv_taps), role="vector", init="normal")})
         if s.bias:
-            out.update({f"{p}.q_proj.bias": TensorSpec((q,), role="matrix"),
-                        f"{p}.k_proj.bias": TensorSpec((kv,), role="matrix"),
-                        f"{p}.v_proj.bias": TensorSpec((kv,), role="matrix"),
-                        f"{p}.o_proj.bias": TensorSpec((s.hidden_size,), role="matrix")})
+            out.update({f"{p}.{s.name('q_bias')}": TensorSpec((q,), role="matrix"),
+                        f"{p}.{s.name('k_bias')}": TensorSpec((kv,), role="matrix"),
+                        f"{p}.{s.name('v_bias')}": TensorSpec((s.num_kv_heads * s.value_dim,), role="matrix")})
+            if s.out_bias:
+                out[f"{p}.{s.name('o_bias')}"] = TensorSpec((s.hidden_size,), role="matrix")
         if s.qk_norm:
-            out.update({f"{p}.q_norm.weight": TensorSpec((s.head_dim,), role="vector", init="gain"),
-                        f"{p}.k_norm.weight": TensorSpec((s.head_dim,), role="vector", init="gain")})
+            out.update({f"{p}.{s.name('q_norm')}": TensorSpec((s.head_dim,), role="vector", init="gain"),
+                        f"{p}.{s.name('k_norm')}": TensorSpec((s.head_dim,), role="vector", init="gain")})
+        if s.talk:
+            out[f"{p}.{s.name('talk')}"] = TensorSpec((s.num_heads, s.num_heads), role="vector", init="mixing")
+        if s.v_share:
+            out[f"{p}.{s.name('v_blend')}"] = TensorSpec((), role="vector", init="half")
         return out
 
     def load(self, get) -> None:
@@ -165,11 +189,17 @@ class Attention(Mixer):
                 wc[1] = wc[1].view(s.num_kv_heads, s.head_dim, -1)[:, order].reshape(kv, -1)
             self.conv_w = torch.cat(wc).contiguous()                       # [q | k | v channels, taps], float32
         if s.bias:
-            self.b_qkv = torch.cat([get(f"{p}.{n}_proj.bias") for n in "qkv"]).contiguous()
-            self.b_o = get(f"{p}.o_proj.bias").contiguous()
+            self.b_qkv = torch.cat([get(f"{p}.{s.name(n + '_bias')}") for n in "qkv"]).contiguous()
+            if s.out_bias:
+                self.b_o = get(f"{p}.{s.name('o_bias')}").contiguous()
+        if s.talk:
+            self.talk = get(f"{p}.{s.name('talk')}").float().contiguous()        # the weights and their mixing are float32
+        if s.v_share:
+            blend = get(f"{p}.{s.name('v_blend')}")                              # the first layer's is loaded and not used
+            self.v_blend = float(blend.float().item()) if s.v_share == "blend" else None
         if s.qk_norm:
-            self.q_gain = get(f"{p}.q_norm.weight")
-            self.k_gain = get(f"{p}.k_norm.weight")
+            self.q_gain = get(f"{p}.{s.name('q_norm')}")
+            self.k_gain = get(f"{p}.{s.name('k_norm')}")
             if self.q_gain.dtype != self.k_gain.dtype:
                 self.q_gain, self.k_gain = self.q_gain.float(), self.k_gain.float()
 
@@ -180,11 +210,16 @@ class Attention(Mixer):
         shared by every layer with the same sizes (``batch.plan``)."""
         s, ops = self.spec, self.ctx.ops
         key = ("attention", group, s.num_heads, s.num_kv_heads, s.head_dim, dtype, page, s.value_dim, bool(s.softcap),
-               bool(s.keep_first), bool(s.conv_taps))
+               bool(s.keep_first), bool(s.conv_taps), s.sink, s.talk)
         sized = {} if s.value_dim == s.head_dim else {"dv": s.value_dim}      # options go to the kernels' faces only
         capped = {"softcap": s.softcap} if s.softcap else {}                  # where the spec sets them
         if s.keep_first:
             sized = dict(sized, keep_first=int(s.keep_first))
+        tiled = dict(sized)
+        if s.sink or s.talk:
+            # options of the CUDA-core kernels; with mixed heads a query head's output row spans all kv heads' values
+            sized = dict(sized, cuda_cores=True, dv=s.num_kv_heads * s.value_dim if s.talk else s.value_dim)
+            tiled = dict(tiled, sink=s.sink, all_values=s.talk)
 
         def make(b):
             nd = b.num_decode
@@ -193,11 +228,12 @@ class Attention(Mixer):
             if decode != ops.plan_decode_attention(dtype, nd, s.num_heads, s.num_kv_heads, s.head_dim, b.max_decode_len,
                                                    even=not b.decode_even, **sized):
                 b.even_asked = True              # a captured step with this plan serves batches of this kind only
-            if s.conv_taps and decode.fused:
-                decode = dataclasses.replace(decode, fused=False)     # the convolution stands between projection and rotation
+            if (s.conv_taps or s.v_norm or s.v_share) and decode.fused:
+                # something stands between projection and rotation, or the values are not cached as projected
+                decode = dataclasses.replace(decode, fused=False)
             rows = tiles = None
             if b.num_requests > nd:
-                rows = ops.prefill_tile_rows(dtype, s.head_dim, page, b.num_tokens - nd, **capped, **sized)
+                rows = ops.prefill_tile_rows(dtype, s.head_dim, page, b.num_tokens - nd, **capped, **tiled)
                 tiles = ops.prefill_tiles(b.h_prefix_lens, b.h_new_lens, nd, rows, b.token_ids.device)
             return AttentionPlan(decode, rows, tiles)
         return batch.plan(key, make)
@@ -209,6 +245,8 @@ class Attention(Mixer):
         sized = {} if dv == s.head_dim else {"dv": dv}
         capped = {"softcap": s.softcap} if s.softcap else {}
         kept = {"keep_first": int(s.keep_first)} if s.keep_first else {}
+        if s.sink or s.talk:
+            kept = dict(kept, sink=s.sink, all_values=s.talk)
         table = batch.block_tables[cache.group]
         plan = self._plan(batch, cache.group, cache.data.dtype, page)
         if s.conv_taps:
@@ -233,10 +271,23 @@ class Attention(Mixer):
             if gate is not None:
                 ops.sigmoid_gate(out, gate)
             return ops.linear_auto(out, self.w_o, self.b_o)
+        values = {}
+        if s.v_norm or s.v_share:
+            values = {"v_norm": s.v_norm}
+            if s.v_share:
+                # the first sharing layer's values of this step's tokens, float32; the layers behind it read them
+                cols = s.num_kv_heads * dv
+                values["v_keep"] = batch.plan(("first_values", cols), lambda b: torch.empty((b.num_tokens, cols), dtype=torch.float32,
+                                                                                             device=x.device))
+                if s.v_share == "blend":
+                    values["v_blend"] = self.v_blend
         q = ops.qk_norm_rope_write(qkv, self.q_gain, self.k_gain, s.norm_eps, cos, sin, batch.positions,
                                    batch.token_req, table, cache.data, s.num_heads, s.num_kv_heads, s.head_dim,
-                                   rotary_dim, page, write_kv=write_cache, **sized)
-        out = torch.empty((q.shape[0], s.num_heads * dv), dtype=q.dtype, device=q.device)
+                                   rotary_dim, page, write_kv=write_cache, **sized, **values)
+        if s.talk:
+            out = torch.empty((q.shape[0], s.num_heads * s.num_kv_heads * dv), dtype=torch.float32, device=q.device)
+        else:
+            out = torch.empty((q.shape[0], s.num_heads * dv), dtype=q.dtype, device=q.device)
         if nd:
             ops.attention_decode(q[:nd], cache.data, table, batch.seq_lens, out[:nd], scratch, dec.splits,
                                  s.num_heads, s.num_kv_heads, s.head_dim, page, self.scale, s.window, stages=dec.stages,
@@ -248,4 +299,6 @@ class Attention(Mixer):
                                   tile_rows=plan.tile_rows, **capped, **sized, **kept)
         if gate is not None:
             ops.sigmoid_gate(out, gate)
+        if s.talk:
+            out = ops.head_mix(out, self.talk, s.num_heads, s.num_kv_heads, dv, q.dtype)
         return ops.linear_auto(out, self.w_o, self.b_o)

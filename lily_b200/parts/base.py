@@ -51,7 +51,7 @@ class TensorSpec:
                     else is held in the compute dtype.
           "table":  integer tables; held as int32.
     init  how the random-weights mode draws it: "normal" N(0, std), "gain" 1 + N(0, jitter),
-          "zeros".
+          "zeros", "mixing" (a square matrix near the identity), "half" (a weight between 0 and 1).
     short_rows  vocabulary tables: a checkpoint saved before the vocabulary was padded holds fewer rows; they
           are taken and the missing rows are zero (lily/layers/vocab_embedding.py:29-35).
     """
@@ -203,7 +203,8 @@ def _load_builtin_parts() -> None:
     global _BUILTINS
     if not _BUILTINS:
         _BUILTINS = True
-        from lily_b200.parts import attention, block, diff_attention, experts, latent_attention, mlp, norm, rope, ssm, wkv  # noqa: F401
+        from lily_b200.parts import (attention, block, delta_rule, diff_attention, experts, latent_attention, mlp, norm, rope,  # noqa: F401
+                                     selective_scan, ssm, wkv)
 
 
 # --------------------------------------------------------------------------- model description

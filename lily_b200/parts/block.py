@@ -121,7 +121,9 @@ class ParallelBlock(Block):
 class SandwichBlockSpec:
     """A norm ahead of and behind each sublayer: ``r += mult * norm_1b(mixer(norm_1(r)))``, then, where the block has a
     feed-forward, ``r += mult * norm_2b(ff(norm_2(r)))``.  The norm behind a sublayer and the add are folded into the
-    pass of the norm that comes next (``NormedDelta``), in this block or in the one after it."""
+    pass of the norm that comes next (``NormedDelta``), in this block or in the one after it.
+    ``post_divides`` False: what stands behind a sublayer is a gain per column alone (a layer scale,
+    ``r += mult * gain_1b * mixer(norm_1(r))``), named like the norms behind the sublayers and folded the same way."""
 
     prefix: str
     mixer: Any
@@ -132,6 +134,7 @@ class SandwichBlockSpec:
     mixer_name: str = "mix"
     feed_forward_name: str = "mlp"
     norm_names: Tuple[str, str, str, str] = ("norm1", "norm1b", "norm2", "norm2b")
+    post_divides: bool = True
 
 
 @register_part("block", "sandwich")
@@ -166,10 +169,10 @@ class SandwichBlock(Block):
         self.post_gains = [n.weight.float().contiguous() for n in (self.norm_in_post, self.norm_ff_post) if n is not None]
 
     def forward(self, residual, delta, batch, run: RunSlots):
-        eps, mult = self.spec.norm.eps, float(self.spec.mult)
+        eps, mult, divides = self.spec.norm.eps, float(self.spec.mult), self.spec.post_divides
         h = self.norm_in.forward(residual, delta, delta_bias=run.stream_bias)
-        a = NormedDelta(self.mixer.forward(h, batch, run.caches[0], run.states[0], run.write_cache), self.post_gains[0], eps, mult)
+        a = NormedDelta(self.mixer.forward(h, batch, run.caches[0], run.states[0], run.write_cache), self.post_gains[0], eps, mult, divides)
         if self.feed_forward is None:
             return a
         h = self.norm_ff.forward(residual, a)
-        return NormedDelta(self.feed_forward.forward(h, batch), self.post_gains[1], eps, mult)
+        return NormedDelta(self.feed_forward.forward(h, batch), self.post_gains[1], eps, mult, divides)

@@ -26,7 +26,10 @@ class SwiGLUSpec:
     hidden_size: int
     intermediate_size: int
     kind: str = "swiglu"
-    activation: str = "silu"              # "silu" | "gelu_tanh"
+    activation: str = "silu"              # "silu" | "gelu_tanh" | "swish_clamped"
+    # "swish_clamped": down(g sigmoid(alpha g) (u + 1)) with g = min(gate x, limit), u = clamp(up x, -limit, limit)
+    limit: float = 0.0
+    alpha: float = 1.702
     # names of the gate, up and down weights under the part's prefix; None: "<x>_proj.weight"
     names: Optional[Tuple[Tuple[str, str], ...]] = None
 
@@ -54,7 +57,8 @@ class SwiGLU(FeedForward):
         gate = get(f"{p}.{name('gate')}")
         h = self.spec.hidden_size
         self.w_gate_up = torch.empty((2 * i, h), dtype=gate.dtype, device=gate.device)
-        self.block = b = self.ctx.ops.gate_up_interleave(gate.dtype, i)
+        # the clamped form has the stand-alone activation kernel only, which reads [all gate | all up]
+        self.block = b = None if self.spec.activation == "swish_clamped" else self.ctx.ops.gate_up_interleave(gate.dtype, i)
         if b:
             runs = self.w_gate_up.view(i // b, 2, b, h)
             runs[:, 0].copy_(gate.view(i // b, b, h))
@@ -69,6 +73,10 @@ class SwiGLU(FeedForward):
     def forward(self, x, batch):
         ops = self.ctx.ops
         product = ops.linear_auto                                # partial sums for a few tokens, else [M, N]
+        if self.spec.activation == "swish_clamped":
+            act = ops.silu_mul(product(x, self.w_gate_up), x.dtype, activation="swish_clamped", limit=self.spec.limit,
+                               alpha=self.spec.alpha)
+            return product(act, self.w_down)
         how = {} if self.spec.activation == "silu" else {"activation": self.spec.activation}
         few = ops.swiglu_skinny_need(x.shape[0], self.spec.intermediate_size, self.spec.hidden_size, x.dtype, self.block)
         if few is not None and batch.workspace is not None:

@@ -24,6 +24,7 @@ class NormedDelta:
     gain: Any                  # float32 [size]
     eps: float
     mult: float = 1.0
+    normalise: bool = True     # False: ``mult * (delta * gain)``, a gain per column without the division (a layer scale)
 
 
 @dataclass(frozen=True)
@@ -58,7 +59,8 @@ class RMSNorm(Norm):
                 raise ValueError("a normalised delta comes alone: no stream vector and no second norm in the same pass")
             return self.ctx.ops.add_normed_rmsnorm(residual, delta.delta, delta.gain, delta.eps, delta.mult, self.weight,
                                                    self.spec.eps, out_dtype or self.ctx.dtype, rows=rows,
-                                                   write_residual=write_residual and rows is None)
+                                                   write_residual=write_residual and rows is None,
+                                                   **({} if delta.normalise else {"normalise": False}))
         deltas = [d for d in delta if d is not None] if isinstance(delta, (tuple, list)) else ([delta] if delta is not None else [])
         if delta_bias is None and also is None and len(deltas) <= 1:
             return self.ctx.ops.add_rmsnorm(residual, deltas[0] if deltas else None, self.weight, self.spec.eps,

@@ -3,7 +3,7 @@
 Every tensor the architecture expects is drawn from its own generator, seeded by (seed, tensor
 name), so a tensor's values do not depend on the order in which tensors are made or on which
 other tensors exist: "normal" tensors are N(0, std), "gain" tensors 1 + N(0, gain_jitter),
-"zeros" tensors 0.  ``write_random_model`` writes ``config.json`` and ``model.safetensors``;
+"zeros" tensors 0, "mixing" tensors the identity + N(0, std), "half" tensors sigmoid(N(0, 1)).  ``write_random_model`` writes ``config.json`` and ``model.safetensors``;
 ``RandomSource`` hands the same tensors to the loader without a file (on the device when one is
 given, which is how a model of several GB is made in seconds).
 
@@ -40,6 +40,10 @@ def random_tensor(name: str, spec: TensorSpec, seed: int, dtype: torch.dtype, de
     x = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device)
     if spec.init == "gain":
         x = 1.0 + x * gain_jitter
+    elif spec.init == "mixing":                     # a square matrix near the identity
+        x = torch.eye(spec.shape[0], dtype=torch.float32, device=device) + x * std
+    elif spec.init == "half":                       # a blending weight between 0 and 1
+        x = torch.sigmoid(x)
     else:
         x = x * std
     return x.to(dtype)

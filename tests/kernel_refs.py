@@ -86,7 +86,7 @@ def add_rmsnorm_multi(resid, deltas, gains, eps, out_dtype, bias=None, write_res
     return tuple((unit * g.float()).to(out_dtype) for g in gains)
 
 
-def silu_mul(gate_up, out_dtype=None, out=None, block=None, activation="silu"):
+def silu_mul(gate_up, out_dtype=None, out=None, block=None, activation="silu", limit=0.0, alpha=1.0):
     out_dtype = out_dtype or gate_up.dtype
     gate_up = _sum(gate_up)
     i = gate_up.shape[1] // 2
@@ -97,6 +97,9 @@ def silu_mul(gate_up, out_dtype=None, out=None, block=None, activation="silu"):
         g, u = gate_up[:, :i].float(), gate_up[:, i:].float()
     if activation == "gelu_tanh":
         return (0.5 * g * (1 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3))) * u).to(out_dtype)
+    if activation == "swish_clamped":
+        g, u = torch.clamp(g, max=limit), torch.clamp(u, min=-limit, max=limit)
+        return ((g / (1 + torch.exp(-alpha * g))) * (u + 1)).to(out_dtype)
     assert activation == "silu"
     return ((g / (1 + torch.exp(-g))) * u).to(out_dtype)
 
@@ -113,7 +116,7 @@ def _pages(kv_layer, nkv, page_size, d, dv, values_in_keys=False):
 
 
 def qk_norm_rope_write(qkv, q_gain, k_gain, eps, cos, sin, positions, token_req, block_table, kv_layer, nq, nkv, d,
-                       rotary_dim, page_size, write_kv=True, q_out=None, dv=None):
+                       rotary_dim, page_size, write_kv=True, q_out=None, dv=None, v_norm=False, v_keep=None, v_blend=None):
     qkv = _sum(qkv)
     n = qkv.shape[0]
     dv = dv or d
@@ -139,6 +142,12 @@ def qk_norm_rope_write(qkv, q_gain, k_gain, eps, cos, sin, positions, token_req,
     q = rot(norm(q, q_gain))
     if write_kv:
         k = rot(norm(k, k_gain))
+        if v_norm:
+            v = v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)
+        if v_keep is not None and v_blend is None:
+            v_keep.copy_(v.reshape(n, nkv * dv))
+        elif v_keep is not None:
+            v = (1.0 - v_blend) * v + v_blend * v_keep.view(n, nkv, dv)
         pos = positions.long()
         page = block_table[token_req.long(), pos // page_size].long()
         within = pos % page_size
@@ -212,7 +221,7 @@ def uses_tensor_cores(dtype, d):
 
 
 def prefill_tile_rows(dtype=None, d=0, page_size=0, new_tokens=0, softcap=None, dv=None, values_in_keys=False, heads=0,
-                      keep_first=0):
+                      keep_first=0, sink=False, all_values=False):
     return 32
 
 
@@ -236,11 +245,11 @@ class DecodePlan:
 
 
 def plan_decode_attention(dtype, requests, nq, nkv, d, max_seq_len, even=False, dv=None, values_in_keys=False,
-                          keep_first=0, fusable=True):
+                          keep_first=0, fusable=True, cuda_cores=False):
     if requests == 0:
         return DecodePlan(1, False, 0, "single")
     splits = 2 if max_seq_len >= 32 else 1
-    fused = FUSE_DECODE and (dv or d) == d and fusable and not keep_first
+    fused = FUSE_DECODE and (dv or d) == d and fusable and not keep_first and not cuda_cores
     return DecodePlan(splits, fused, decode_scratch_floats(requests, nq, dv or d, splits), "wave" if splits > 1 else "single")
 
 
@@ -257,8 +266,10 @@ def _gather_kv(kv_layer, table_row, length, page_size, nkv=None, d=None, dv=None
     return k.float(), v.float()
 
 
-def _attend(q, k, v, q_pos, scale, window, softcap=None, keep_first=0):
-    """q [rows, nq, d] at positions q_pos [rows]; k [keys, nkv, d], v [keys, nkv, dv] at positions 0..keys-1."""
+def _attend(q, k, v, q_pos, scale, window, softcap=None, keep_first=0, sink=False, all_values=False):
+    """q [rows, nq, d] at positions q_pos [rows]; k [keys, nkv, d], v [keys, nkv, dv] at positions 0..keys-1.
+    ``sink``: a key of score 0 without a value joins the softmax; ``all_values``: every query head's weights over the
+    values of every kv head, [rows, nq, nkv * dv]."""
     rep = q.shape[1] // k.shape[1]
     kk, vv = k.repeat_interleave(rep, 1), v.repeat_interleave(rep, 1)
     s = torch.einsum("qhd,khd->hqk", q, kk) * scale
@@ -269,31 +280,38 @@ def _attend(q, k, v, q_pos, scale, window, softcap=None, keep_first=0):
     if window:
         seen &= (kpos[None, :] > q_pos[:, None] - window) | (kpos[None, :] < keep_first)
     s = s.masked_fill(~seen[None], float("-inf"))
-    return torch.einsum("hqk,khd->qhd", torch.softmax(s, -1), vv)
+    if sink:
+        p = torch.softmax(torch.cat([s, torch.zeros_like(s[..., :1])], -1), -1)[..., :-1]
+    else:
+        p = torch.softmax(s, -1)
+    if all_values:
+        return torch.einsum("hqk,kgd->qhgd", p, v).reshape(q.shape[0], q.shape[1], -1)
+    return torch.einsum("hqk,khd->qhd", p, vv)
 
 
 def attention_prefill(q, kv_layer, block_table, cu_seqlens, prefix_lens, tile_req, tile_start, out, nq, nkv, d,
                       page_size, scale, window=None, tile_rows=None, heads_per_block=0, softcap=None, dv=None,
-                      values_in_keys=False, keep_first=0):
+                      values_in_keys=False, keep_first=0, sink=False, all_values=False):
     dv = dv or d
     for r in sorted(set(tile_req.tolist())):
         t0, t1 = int(cu_seqlens[r]), int(cu_seqlens[r + 1])
         prefix = int(prefix_lens[r])
         k, v = _gather_kv(kv_layer, block_table[r], prefix + t1 - t0, page_size, nkv, d, dv, values_in_keys)
         qpos = torch.arange(prefix, prefix + t1 - t0, device=q.device)
-        o = _attend(q[t0:t1].float().view(-1, nq, d), k, v, qpos, scale, window, softcap, keep_first)
-        out[t0:t1] = o.reshape(t1 - t0, nq * dv).to(out.dtype)
+        o = _attend(q[t0:t1].float().view(-1, nq, d), k, v, qpos, scale, window, softcap, keep_first, sink, all_values)
+        out[t0:t1] = o.reshape(t1 - t0, -1).to(out.dtype)
 
 
 def attention_decode(q, kv_layer, block_table, seq_lens, out, scratch, splits, nq, nkv, d, page_size, scale,
-                     window=None, stages=0, softcap=None, dv=None, values_in_keys=False, keep_first=0):
+                     window=None, stages=0, softcap=None, dv=None, values_in_keys=False, keep_first=0, sink=False,
+                     all_values=False):
     dv = dv or d
     for r in range(q.shape[0]):
         n = int(seq_lens[r])
         k, v = _gather_kv(kv_layer, block_table[r], n, page_size, nkv, d, dv, values_in_keys)
         o = _attend(q[r:r + 1].float().view(1, nq, d), k, v, torch.tensor([n - 1], device=q.device), scale, window, softcap,
-                    keep_first)
-        out[r] = o.reshape(nq * dv).to(out.dtype)
+                    keep_first, sink, all_values)
+        out[r] = o.reshape(-1).to(out.dtype)
 
 
 def attention_decode_fused(qkv, q_gain, k_gain, eps, cos, sin, kv_layer, block_table, seq_lens, out, scratch, splits, nq, nkv,
@@ -586,10 +604,14 @@ def moe_experts(h, routing, w_gate_up, w_down, limit, alpha):
 
 # ---------------------------------------------------------------------------- sandwich norms, plain feed-forward
 
-def add_normed_rmsnorm(resid, delta, post_gain, post_eps, mult, weight, eps, out_dtype, rows=None, write_residual=True):
-    """resid += mult * (delta / rms(delta) * post_gain); returns (the new rows) / rms * weight (None without ``weight``)."""
+def add_normed_rmsnorm(resid, delta, post_gain, post_eps, mult, weight, eps, out_dtype, rows=None, write_residual=True,
+                       normalise=True):
+    """resid += mult * (delta / rms(delta) * post_gain), or mult * (delta * post_gain) without ``normalise``; returns
+    (the new rows) / rms * weight (None without ``weight``)."""
     d = _sum(delta).float()
-    add = mult * ((d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + post_eps)) * post_gain.float())
+    if normalise:
+        d = d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + post_eps)
+    add = mult * (d * post_gain.float())
     if rows is not None:
         v = resid[rows.long()] + add[rows.long()]
     else:
@@ -655,3 +677,67 @@ def diff_combine(maps_out, proj, gate_col, heads, dv, maps, lam, out_scale, eps)
     o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps) * out_scale
     gate = torch.sigmoid(proj[:, gate_col:gate_col + heads].float())
     return (o * gate[:, :, None]).reshape(n, heads * dv).to(maps_out.dtype)
+
+
+# ---------------------------------------------------------------------------- mixed heads, delta rule, selective scan
+
+def head_mix(sums, mix, nq, nkv, dv, out_dtype):
+    """out[t, h] = sum_g mix[h, g] sums[t, g, kv(h)]; sums float32 [tokens, nq * nkv * dv]."""
+    n = sums.shape[0]
+    own = sums.view(n, nq, nkv, dv)[:, :, torch.arange(nq, device=sums.device) // (nq // nkv)]       # [n, g, h, dv]
+    return torch.einsum("hg,nghd->nhd", mix.float(), own).reshape(n, nq * dv).to(out_dtype)
+
+
+def delta_rule_max_head_dim():
+    return 256
+
+
+def delta_rule(qkv, proj, b_col, a_col, a_log, dt_bias, state, cu_seqlens, slots, requests, heads, kv_heads, d, dv, unit_eps,
+               q_scale):
+    n = qkv.shape[0]
+    x = qkv.float()
+    q = x[:, :kv_heads * d].view(n, kv_heads, d)
+    k = x[:, kv_heads * d:2 * kv_heads * d].view(n, kv_heads, d)
+    v = x[:, 2 * kv_heads * d:].view(n, heads, dv)
+    q = q / torch.sqrt(q.pow(2).sum(-1, keepdim=True) + unit_eps) * q_scale
+    k = k / torch.sqrt(k.pow(2).sum(-1, keepdim=True) + unit_eps)
+    beta = torch.sigmoid(proj[:, b_col:b_col + heads].float())
+    decay = torch.exp(-torch.exp(a_log.float()) * torch.nn.functional.softplus(proj[:, a_col:a_col + heads].float() + dt_bias.float()))
+    y = torch.zeros((n, heads * dv), dtype=torch.float32, device=qkv.device)
+    for r in range(requests):
+        t0, t1 = int(cu_seqlens[r]), int(cu_seqlens[r + 1])
+        row = state[int(slots[r])]
+        S = row[:heads * dv * d].view(heads, dv, d).clone()                       # a head's matrix as [dv, d]
+        for t in range(t0, t1):
+            for h in range(heads):
+                g = h // (heads // kv_heads)
+                Sh = decay[t, h] * S[h]
+                u = beta[t, h] * (v[t, h] - Sh @ k[t, g])
+                S[h] = Sh + torch.outer(u, k[t, g])
+                y[t, h * dv:(h + 1) * dv] = S[h] @ q[t, g]
+        if t1 > t0:
+            row[:heads * dv * d] = S.reshape(-1)
+    return y
+
+
+def selective_scan_max_state():
+    return 256
+
+
+def selective_scan(x, low, b_col, step, proj, z_col, a, d_skip, state, cu_seqlens, slots, requests):
+    tokens, inner = x.shape
+    n = a.shape[1]
+    xf, dt = x.float(), torch.nn.functional.softplus(step.float())
+    B, C = low[:, b_col:b_col + n].float(), low[:, b_col + n:b_col + 2 * n].float()
+    z = proj[:, z_col:z_col + inner].float()
+    out = torch.zeros((tokens, inner), dtype=torch.float32, device=x.device)
+    for r in range(requests):
+        t0, t1 = int(cu_seqlens[r]), int(cu_seqlens[r + 1])
+        row = state[int(slots[r])]
+        S = row[:inner * n].view(inner, n).clone()
+        for t in range(t0, t1):
+            S = torch.exp(dt[t][:, None] * a.float()) * S + (dt[t] * xf[t])[:, None] * B[t][None, :]
+            out[t] = (S @ C[t] + d_skip.float() * xf[t]) * (z[t] / (1 + torch.exp(-z[t])))
+        if t1 > t0:
+            row[:inner * n] = S.reshape(-1)
+    return out.to(x.dtype)

@@ -39,9 +39,12 @@ struct DeltaArgs {
     float unit_eps, q_scale;
 };
 
+// Sum over the DL lanes of a column.  The mask names those lanes only: the two groups of a warp may stand in
+// different turns of a loop (a tile whose tokens do not divide among the groups).
 __device__ __forceinline__ float sum_over_lanes(float v) {
+    const unsigned mask = (DL == 32 ? 0xffffffffu : ((1u << DL) - 1u)) << ((threadIdx.x & 31) / DL * DL);
 #pragma unroll
-    for (int o = DL / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    for (int o = DL / 2; o > 0; o >>= 1) v += __shfl_xor_sync(mask, v, o);
     return v;
 }
 

@@ -93,7 +93,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) selective_scan_kernel(const Sele
                 acc = fmaf(S[r], Cs[t][l + SL * r], acc);
             }
 #pragma unroll
-            for (int o = SL / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+            for (int o = SL / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);      // every thread of the block is in this turn
             if (l == 0) {
                 const float zv = zs[t][cg];
                 ys[t][cg] = fmaf(skip, xv, acc) * (zv / (1.f + expf(-zv)));

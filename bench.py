@@ -5,6 +5,7 @@ tokens a second at 2,048 tokens, for the Qwen3-8B layer sizes with random weight
     python bench.py --design zirurax [--sizes small mid] [--layers L]      (another design beside the dense decoder)
     python bench.py --design godotar [--sizes small mid] [--layers L]      (the same for the Godotar decoder)
     python bench.py --design gotivik [--sizes small mid] [--layers L]      (the same for the Gotivik decoder)
+    python bench.py --design kinanex [--sizes small mid] [--layers L]      (the Kinanex decoder beside the Zirurax and the dense one)
 
 Prints one JSON line.  A step is one decode step of the whole batch.  After W untimed steps, ``value``
 times K steps of the engine's step function plus the argmax kernel on the device (CUDA events; the tokens
@@ -239,14 +240,14 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the model has (reported)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true", help="leave out the batch 1 and 64 points")
-    ap.add_argument("--design", default=None, choices=["zirurax", "godotar", "gotivik"],
+    ap.add_argument("--design", default=None, choices=["zirurax", "godotar", "gotivik", "kinanex"],
                     help="instead of the headline: this design beside the dense decoder at equal sizes, models and kernels "
-                         "(lily_b200/bench/design_bench.py, godotar_bench.py, gotivik_bench.py; --layers, --batch and --steps apply)")
+                         "(lily_b200/bench/design_bench.py, godotar_bench.py, gotivik_bench.py, kinanex_bench.py; --layers, --batch and --steps apply)")
     ap.add_argument("--sizes", nargs="+", default=["small", "mid"], help="--design: which of its sizes")
     a = ap.parse_args()
     if a.design:
-        from lily_b200.bench import design_bench, godotar_bench, gotivik_bench
-        out = {"godotar": godotar_bench, "gotivik": gotivik_bench, "zirurax": design_bench}[a.design].run(a.sizes, min(a.layers, 4) if a.layers == FULL_LAYERS else a.layers, PREFILL_TOKENS, a.batch,
+        from lily_b200.bench import design_bench, godotar_bench, gotivik_bench, kinanex_bench
+        out = {"godotar": godotar_bench, "gotivik": gotivik_bench, "zirurax": design_bench, "kinanex": kinanex_bench}[a.design].run(a.sizes, min(a.layers, 4) if a.layers == FULL_LAYERS else a.layers, PREFILL_TOKENS, a.batch,
                                CONTEXT, max(1, min(a.steps, 32)))
         print(json.dumps(out))
         return 0

@@ -140,7 +140,8 @@ def kernel_table(z: dict, tokens: int, batch: int, context: int, reps: int = 30,
         # ---- rotation + cache write with normed, blended values beside the plain one (same sizes)
         cols = (nq + nkv) * dd + nkv * dv
         aqkv = [rnd(n, cols).to(dt) for _ in range(copies)]
-        caches = [torch.zeros(reqs * pages_per + 1, nkv * page * (dd + dv), device=dev, dtype=dt) for _ in range(copies)]
+        cache_shape = (reqs * pages_per + 1, 2, nkv, page, dd) if dv == dd else (reqs * pages_per + 1, nkv * page * (dd + dv))
+        caches = [torch.zeros(cache_shape, device=dev, dtype=dt) for _ in range(copies)]
         keeps = [rnd(n, nkv * dv) for _ in range(copies)]
         qg, kg = torch.ones(dd, device=dev), torch.ones(dd, device=dev)
         cos, sin = (torch.rand(per + 1, dd // 4, device=dev, generator=g) for _ in range(2))
@@ -151,6 +152,7 @@ def kernel_table(z: dict, tokens: int, batch: int, context: int, reps: int = 30,
         add("qk_norm_rope_write (like)", "-",
             [lambda x=x, c=c: ops.qk_norm_rope_write(x, qg, kg, 1e-6, cos, sin, positions, token_req, table, c, nq, nkv, dd, dd // 2, page, dv=dv)
              for x, c in zip(aqkv, caches)], n * (cols * 2 + nq * dd * 2 + nkv * (dd + dv) * 2), shape=label)
+        sized = {} if dv == dd else {"dv": dv}
         sums = [rnd(n, nq * nkv * dv) for _ in range(copies)]
         mix = torch.eye(nq, device=dev) + rnd(nq, nq) / 8
         add("head_mix", "sigmoid_gate", [lambda s=s: ops.head_mix(s, mix, nq, nkv, dv, dt) for s in sums], n * nq * dv * (nkv * 4 + 2),

@@ -9,8 +9,8 @@ Random weights in bfloat16.  A size gives all models the same width, layers and 
 alternate as [delta, attention + feed-forward, mamba1, attention + feed-forward]: the delta rule has the size's heads
 with keys and values of the size's head width (its state is heads x head x head float32 a request); the selective scan
 has 2 x width channels of 16 state entries and a step rank of width / 16; the attention has the size's heads with keys
-of the head width, biases, q/k norm, half of the head rotated, values of 512 / kv_heads columns at most (a query row of
-the kernel gathers the values of all kv heads, and 512 columns are its limit), the sink and mixed heads; the
+and values of the head width, biases, q/k norm, half of the head rotated, the sink and mixed heads (the kernel table also
+has the attention with values of 48 columns, a shape the CUDA-core kernels take); the
 feed-forward has the dense layer's width.
 Timing as in ``design_bench``: device time by CUDA events after warm-up, weights and caches larger than L2, kernels
 over rotated inputs replayed from a graph.
@@ -32,7 +32,7 @@ SCAN_STATE = 16
 
 
 def value_dim(z: dict) -> int:
-    return min(z["head"], 512 // z["kv_heads"])
+    return z["head"]
 
 
 def kinanex_config(z: dict, layers: int) -> dict:
@@ -172,11 +172,12 @@ def kernel_table(z: dict, tokens: int, batch: int, context: int, reps: int = 30,
             cache = rnd(*shape).to(dt)
             tbl = (torch.randperm(pages, device=dev, generator=g) + 1).view(1, pages).to(torch.int32)
             q = rnd(tokens, nq * dd).to(dt)
-            out = torch.empty((tokens, nq * wide), device=dev, dtype=torch.float32 if how.get("all_values") else dt)
+            out = ops.all_values_sums(dt, tokens, nq, nkv, dd, d_v, dev) if how.get("all_values") else torch.empty((tokens, nq * d_v), device=dev, dtype=dt)
             tile = ops.prefill_tile_rows(dt, dd, page, tokens, **sized, **how)
             tr, ts = ops.prefill_tiles([0], [tokens], 0, tile, dev)
             fns.append(lambda q=q, cache=cache, tbl=tbl, out=out, tr=tr, ts=ts, tile=tile: ops.attention_prefill(
                 q, cache, tbl, cu1, pre, tr, ts, out, nq, nkv, dd, page, dd ** -0.5, None, tile_rows=tile, **sized, **how))
+        # the work counted is the design's own: scores once, weighted sums over every kv head's values
         add(name, like, fns, tokens * (nkv * (dd + d_v) + nq * dd) * 2 + tokens * nq * wide * out.element_size(),
             2.0 * nq * (dd + wide) * pairs, shape=f"{tokens} tokens")
 
@@ -190,10 +191,11 @@ def kernel_table(z: dict, tokens: int, batch: int, context: int, reps: int = 30,
             cache = rnd(*shape).to(dt)
             tbl = (torch.randperm(batch * pages, device=dev, generator=g) + 1).view(batch, pages).to(torch.int32)
             q = rnd(batch, nq * dd).to(dt)
-            out = torch.empty((batch, nq * wide), device=dev, dtype=torch.float32 if how.get("all_values") else dt)
+            out = ops.all_values_sums(dt, batch, nq, nkv, dd, d_v, dev) if how.get("all_values") else torch.empty((batch, nq * d_v), device=dev, dtype=dt)
             seq = torch.full((batch,), context, device=dev, dtype=torch.int32)
+            on_cores = bool(how) and not ops.sink_on_tensor_cores(dt, dd, d_v)
             plan = ops.plan_decode_attention(dt, batch, nq, nkv, dd, context, fusable=False,
-                                             **({"dv": wide, "cuda_cores": True} if how else sized))
+                                             **({"dv": wide, "cuda_cores": True} if on_cores else sized))
             scratch = torch.empty(max(1, plan.scratch_floats), device=dev)
             fns.append(lambda q=q, cache=cache, tbl=tbl, out=out, seq=seq, scratch=scratch, plan=plan: ops.attention_decode(
                 q, cache, tbl, seq, out, scratch, plan.splits, nq, nkv, dd, page, dd ** -0.5, None, stages=plan.stages, **sized, **how))
@@ -201,11 +203,15 @@ def kernel_table(z: dict, tokens: int, batch: int, context: int, reps: int = 30,
             shape=f"{batch} x {context}")
 
     prefill("attention_prefill (sink, values of all kv heads)", "attention_prefill", dv, sink=True, all_values=True)
-    prefill("attention_prefill (sink alone, CUDA cores)", "attention_prefill", dv, sink=True)
-    prefill("attention_prefill (dense heads, tensor cores)", "-", dd)
+    prefill("attention_prefill (sink alone)", "attention_prefill", dv, sink=True)
+    prefill("attention_prefill (dense heads)", "-", dd)
     decode("attention_decode (sink, values of all kv heads)", "attention_decode", dv, sink=True, all_values=True)
-    decode("attention_decode (sink alone, CUDA cores)", "attention_decode", dv, sink=True)
-    decode("attention_decode (dense heads, tensor cores)", "-", dd)
+    decode("attention_decode (sink alone)", "attention_decode", dv, sink=True)
+    decode("attention_decode (dense heads)", "-", dd)
+    if dv != 48:
+        # a value size of its own (keys 128 / values 48 a head): the CUDA-core kernels take these shapes
+        prefill("attention_prefill (sink, all kv heads; values of 48: CUDA cores)", "attention_prefill", 48, sink=True, all_values=True)
+        decode("attention_decode (sink, all kv heads; values of 48: CUDA cores)", "attention_decode", 48, sink=True, all_values=True)
     return rows
 
 

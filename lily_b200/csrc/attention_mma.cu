@@ -186,6 +186,8 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
     auto tile_limit = [&](int t) { return t < ftiles ? kept : kend; };
 
     const __nv_bfloat16* kv_head = kv + (size_t)kvh * head_stride;
+    // the values lie nkv heads behind the keys; with v_shift, those of another kv head
+    const size_t v_off = (size_t)(a.nkv + (a.v_shift ? (kvh + a.v_shift) % a.nkv - kvh : 0)) * head_stride;
     const int page_mask = (1 << page_shift) - 1;
     auto load_tile = [&](int t, int buf) {
         const int kb = tile_base(t), klim = tile_limit(t);
@@ -200,7 +202,7 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
             const __nv_bfloat16* src = kv_head + (size_t)page * page_stride + (((ok ? kpos : 0) & page_mask) * D + ch * 8);
             const uint32_t off = swz<D>(r, ch);
             cp_async16(smem_u32(kd + off), src, ok);
-            cp_async16(smem_u32(vd + off), src + (size_t)a.nkv * head_stride, ok);
+            cp_async16(smem_u32(vd + off), src + v_off, ok);
         }
     };
 
@@ -411,7 +413,10 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
     const int row_hi = row_lo + 8;
     const int qpos_lo = DECODE ? pos0 : pos0 + row_lo, qpos_hi = DECODE ? pos0 : pos0 + row_hi;
 
-    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+    // the sink: a key of score 0 without a value, counted once a row (decode: by the first warp of the first key range;
+    // the sums are per thread until the end, so one thread of the four that share a row holds the unit)
+    const bool sunk = a.sink && (!DECODE || (warp == 0 && blockIdx.z == 0));
+    float m_lo = sunk ? 0.f : -INFINITY, m_hi = m_lo, l_lo = sunk && c == 0 ? 1.f : 0.f, l_hi = l_lo;
     float o[D / 8][4];
 #pragma unroll
     for (int j = 0; j < D / 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
@@ -828,15 +833,16 @@ LILY_API int lily_attention_prefill_mma(const void* q, const void* kv, void* out
                                         int bt_stride, const int* cu_seqlens, const int* prefix_lens,
                                         const int* tile_req, const int* tile_start, int tiles, int nq, int nkv,
                                         int d, int page_size, int window, float scale, float softcap,
-                                        int keep_first, cudaStream_t stream) {
+                                        int keep_first, int sink, int v_shift, cudaStream_t stream) {
     if (tiles == 0) return 0;
     LILY_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_prefill: %d query heads over %d kv heads", nq, nkv);
+    LILY_REQUIRE(v_shift >= 0 && v_shift < nkv, "attention_prefill: value heads shifted by %d of %d", v_shift, nkv);
     LILY_REQUIRE(nq <= 65535 && page_size > 0, "attention_prefill: nq=%d page_size=%d", nq, page_size);
     AttnArgs a{};
     a.q = q; a.kv = kv; a.out = out; a.block_table = block_table; a.bt_stride = bt_stride;
     a.cu_seqlens = cu_seqlens; a.prefix_lens = prefix_lens; a.tile_req = tile_req; a.tile_start = tile_start;
     a.splits = 1; a.nq = nq; a.nkv = nkv; a.d = d; a.page_size = page_size; a.window = window; a.scale = scale;
-    a.softcap = softcap;
+    a.softcap = softcap; a.sink = sink; a.v_shift = v_shift;
     a.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
     bool merged = false;
     int rc = mma::dispatch<false>(a, dim3(tiles, nq), stream, &merged);
@@ -893,9 +899,10 @@ static int decode_mma(AttnArgs& a, const void* q, const void* kv, void* out, con
 LILY_API int lily_attention_decode_mma(const void* q, const void* kv, void* out, const int* block_table,
                                        int bt_stride, const int* seq_lens, float* scratch, int requests, int splits,
                                        int nq, int nkv, int d, int page_size, int window, float scale, int stages,
-                                       float softcap, int keep_first, cudaStream_t stream) {
+                                       float softcap, int keep_first, int sink, int v_shift, cudaStream_t stream) {
     AttnArgs a{};
-    a.softcap = softcap;
+    LILY_REQUIRE(nkv > 0 && v_shift >= 0 && v_shift < nkv, "attention_decode: value heads shifted by %d of %d", v_shift, nkv);
+    a.softcap = softcap; a.sink = sink; a.v_shift = v_shift;
     a.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
     return decode_mma(a, q, kv, out, block_table, bt_stride, seq_lens, scratch, requests, splits, nq, nkv, d, page_size,
                       window, scale, stages, stream);

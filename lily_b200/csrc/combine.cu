@@ -56,21 +56,31 @@ __global__ void sigmoid_gate_bf16x8_kernel(__nv_bfloat16* __restrict__ out, cons
 }
 
 // The heads' attention weights mixed by a matrix, applied behind the weighted sums: `in` holds, for every query head g,
-// its weights' sums over the values of every kv head, [tokens][nq][nkv][dv] in float32; head h takes the sums over its
-// own kv head's values from all query heads.  One block a token; the matrix [nq][nq] in shared memory.
-template <typename T>
-__global__ void head_mix_kernel(const float* __restrict__ in, const float* __restrict__ mix, T* __restrict__ out, int nq, int nkv, int dv) {
+// its weights' sums over the values of every kv head; head h takes the sums over its own kv head's values from all query
+// heads.  Two layouts of `in`: rows [tokens][nq][nkv][dv] (float32, the CUDA-core attention kernel's), or planes
+// [nkv][tokens][nq][dv] where plane s holds, for a head of kv head g, the sums over kv head (g + s) % nkv (one launch of
+// the mma.sync attention kernel a plane).  One block a token; the matrix [nq][nq] in shared memory.
+template <typename T, typename IN>
+__global__ void head_mix_kernel(const IN* __restrict__ in, int planes, size_t plane_stride, const float* __restrict__ mix,
+                                T* __restrict__ out, int nq, int nkv, int dv) {
     extern __shared__ float mix_s[];
     pdl_enter_small();
     for (int i = threadIdx.x; i < nq * nq; i += blockDim.x) mix_s[i] = mix[i];
     __syncthreads();
     const int group = nq / nkv;
-    const float* row = in + (size_t)blockIdx.x * nq * nkv * dv;
     for (int e = threadIdx.x; e < nq * dv; e += blockDim.x) {
-        const int h = e / dv, c = e % dv;
-        const float* src = row + (size_t)(h / group) * dv + c;
+        const int h = e / dv, c = e % dv, own = h / group;
         float acc = 0.f;
-        for (int g = 0; g < nq; ++g) acc = fmaf(mix_s[h * nq + g], src[(size_t)g * nkv * dv], acc);
+        if (planes) {
+            const IN* row = in + (size_t)blockIdx.x * nq * dv + c;
+            for (int g = 0; g < nq; ++g) {
+                const int s = (own - g / group + nkv) % nkv;               // the plane in which head g looked at kv head `own`
+                acc = fmaf(mix_s[h * nq + g], to_float(row[(size_t)s * plane_stride + (size_t)g * dv]), acc);
+            }
+        } else {
+            const IN* src = in + (size_t)blockIdx.x * nq * nkv * dv + (size_t)own * dv + c;
+            for (int g = 0; g < nq; ++g) acc = fmaf(mix_s[h * nq + g], to_float(src[(size_t)g * nkv * dv]), acc);
+        }
         out[(size_t)blockIdx.x * nq * dv + e] = from_float<T>(acc);
     }
 }
@@ -210,16 +220,20 @@ LILY_API int lily_sigmoid_gate(void* out, int out_dtype, const void* gate, int g
     return 0;
 }
 
-LILY_API int lily_head_mix(const float* in, const float* mix, void* out, int tokens, int nq, int nkv, int dv, int out_dtype,
-                           cudaStream_t stream) {
+LILY_API int lily_head_mix(const void* in, int in_dtype, int planes, const float* mix, void* out, int tokens, int nq, int nkv,
+                           int dv, int out_dtype, cudaStream_t stream) {
     if (tokens == 0) return 0;
     LILY_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0 && dv > 0, "head_mix: %d heads over %d kv heads of %d value columns", nq, nkv, dv);
+    LILY_REQUIRE(planes || in_dtype == kF32, "head_mix: rows of sums over all kv heads are float32");
     const size_t smem = sizeof(float) * (size_t)nq * nq;
     LILY_REQUIRE(smem <= 48 * 1024, "head_mix: a matrix over %d heads does not fit shared memory", nq);
     int threads = (nq * dv + 31) / 32 * 32;
     threads = threads > 256 ? 256 : threads;
-    if (out_dtype == kBF16) launch_pdl(head_mix_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), smem, stream, in, mix, (__nv_bfloat16*)out, nq, nkv, dv);
-    else launch_pdl(head_mix_kernel<float>, dim3(tokens), dim3(threads), smem, stream, in, mix, (float*)out, nq, nkv, dv);
+    const size_t plane = (size_t)tokens * nq * dv;
+#define GO(T, IN) launch_pdl(head_mix_kernel<T, IN>, dim3(tokens), dim3(threads), smem, stream, (const IN*)in, planes, plane, mix, (T*)out, nq, nkv, dv)
+    if (out_dtype == kBF16) { if (in_dtype == kBF16) GO(__nv_bfloat16, __nv_bfloat16); else GO(__nv_bfloat16, float); }
+    else { if (in_dtype == kBF16) GO(float, __nv_bfloat16); else GO(float, float); }
+#undef GO
     LILY_CHECK_LAUNCH("head_mix");
     return 0;
 }

@@ -12,7 +12,8 @@
 //
 //     u_j = b (v_j - a (S^T k)_j),    o_j = a (S^T q)_j + (k . q) u_j,    S_ij <- a S_ij + k_i u_j
 //
-// then one exchange over the DL lanes and one pass that updates the rows.  Decay, gate, unit vectors, state and sums are
+// then one exchange over the DL lanes and one pass that updates the rows.  The tokens come in tiles of DELTA_TOKENS
+// through shared memory; the next tile's inputs are loaded into registers while the current one is worked on.  Decay, gate, unit vectors, state and sums are
 // float32 whatever the activation dtype.  State row of a slot: [heads][dv][d] (d fastest) at the row's start.
 #include "common.cuh"
 
@@ -49,7 +50,9 @@ __device__ __forceinline__ float sum_over_lanes(float v) {
 }
 
 // grid (requests, heads, ceil(dv / DELTA_COLS)), block DELTA_THREADS; d <= DL * R
-template <typename T, int R>
+// AHEAD: a tile's inputs are loaded one tile ahead (portions of prompts); without it they are loaded when their turn
+// comes, which keeps fewer registers alive and more blocks on a SM (steps in which every request brings one token).
+template <typename T, int R, bool AHEAD>
 __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(const DeltaArgs a) {
     constexpr int DP = DL * R;
     __shared__ float qs[DELTA_TOKENS][DP], ks[DELTA_TOKENS][DP];
@@ -74,26 +77,50 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(const DeltaAr
     const T* proj = (const T*)a.proj;
     const int out_stride = a.heads * dv;
 
-    for (int t0 = 0; t0 < len; t0 += DELTA_TOKENS) {
+    // A tile's inputs are asked for into registers one tile ahead, so that they travel while the tile before is worked on.
+    constexpr int PER = DELTA_TOKENS * DP / DELTA_THREADS;          // q (and k) entries a thread stages: 2 R
+    float rq[PER], rk[PER], rv = 0.f, rb = 0.f, ra = 0.f;
+    auto fetch = [&](int t0) {
         const int n = min(DELTA_TOKENS, len - t0);
-        __syncthreads();
-        for (int e = threadIdx.x; e < n * DP; e += DELTA_THREADS) {
-            const int t = e / DP, i = e % DP;
-            const T* row = qkv + (size_t)(tok0 + t0 + t) * a.qkv_stride + (size_t)kvh * d + i;
-            qs[t][i] = i < d ? to_float(row[a.q_col]) : 0.f;
-            ks[t][i] = i < d ? to_float(row[a.k_col]) : 0.f;
+#pragma unroll
+        for (int it = 0; it < PER; ++it) {
+            const int e = it * DELTA_THREADS + threadIdx.x, t = e / DP, i = e % DP;
+            const bool ok = t < n && i < d;
+            const T* row = qkv + (size_t)(tok0 + t0 + (ok ? t : 0)) * a.qkv_stride + (size_t)kvh * d + (ok ? i : 0);
+            rq[it] = ok ? to_float(row[a.q_col]) : 0.f;
+            rk[it] = ok ? to_float(row[a.k_col]) : 0.f;
         }
-        for (int e = threadIdx.x; e < n * DELTA_COLS; e += DELTA_THREADS) {
-            const int t = e / DELTA_COLS, c = e % DELTA_COLS;
-            vs[t][c] = col0 + c < dv ? to_float(qkv[(size_t)(tok0 + t0 + t) * a.qkv_stride + a.v_col + (size_t)head * dv + col0 + c]) : 0.f;
+        {
+            const int t = threadIdx.x / DELTA_COLS, c = threadIdx.x % DELTA_COLS;       // DELTA_TOKENS * DELTA_COLS == DELTA_THREADS
+            rv = t < n && col0 + c < dv ? to_float(qkv[(size_t)(tok0 + t0 + t) * a.qkv_stride + a.v_col + (size_t)head * dv + col0 + c]) : 0.f;
         }
         if (threadIdx.x < n) {
             const T* row = proj + (size_t)(tok0 + t0 + threadIdx.x) * a.proj_stride + head;
-            const float beta = to_float(row[a.b_col]), alpha = to_float(row[a.a_col]) + dt_bias;
-            bs[threadIdx.x] = 1.f / (1.f + expf(-beta));
+            rb = to_float(row[a.b_col]);
+            ra = to_float(row[a.a_col]);
+        }
+    };
+    static_assert(DELTA_TOKENS * DELTA_COLS == DELTA_THREADS, "a thread stages one value of a tile");
+    if (AHEAD) fetch(0);
+
+    for (int t0 = 0; t0 < len; t0 += DELTA_TOKENS) {
+        const int n = min(DELTA_TOKENS, len - t0);
+        if (!AHEAD) fetch(t0);
+        __syncthreads();
+#pragma unroll
+        for (int it = 0; it < PER; ++it) {
+            const int e = it * DELTA_THREADS + threadIdx.x;
+            qs[e / DP][e % DP] = rq[it];
+            ks[e / DP][e % DP] = rk[it];
+        }
+        vs[threadIdx.x / DELTA_COLS][threadIdx.x % DELTA_COLS] = rv;
+        if (threadIdx.x < n) {
+            const float alpha = ra + dt_bias;
+            bs[threadIdx.x] = 1.f / (1.f + expf(-rb));
             as[threadIdx.x] = expf(-rate * (alpha > 20.f ? alpha : log1pf(expf(alpha))));
         }
         __syncthreads();
+        if (AHEAD && t0 + DELTA_TOKENS < len) fetch(t0 + DELTA_TOKENS);
         // q and k of the head as unit vectors: a group of lanes a token
         for (int t = cg; t < n; t += DELTA_COLS) {
             float sq = 0.f, sk = 0.f;
@@ -153,8 +180,8 @@ LILY_API int lily_delta_rule_max_head_dim() { return DL * 16; }
 
 LILY_API int lily_delta_rule(const void* qkv, int qkv_stride, int q_col, int k_col, int v_col, const void* proj, int proj_stride,
                              int b_col, int a_col, const float* a_log, const float* dt_bias, float* state, size_t state_stride,
-                             float* y, const int* cu_seqlens, const int* slots, int requests, int heads, int kv_heads, int d,
-                             int dv, float unit_eps, float q_scale, int dtype, cudaStream_t stream) {
+                             float* y, const int* cu_seqlens, const int* slots, int requests, int tokens, int heads, int kv_heads,
+                             int d, int dv, float unit_eps, float q_scale, int dtype, cudaStream_t stream) {
     if (requests == 0) return 0;
     LILY_REQUIRE(heads > 0 && kv_heads > 0 && heads % kv_heads == 0, "delta_rule: %d heads over %d query/key heads", heads, kv_heads);
     LILY_REQUIRE(d > 0 && d <= DL * 16 && dv > 0, "delta_rule: head sizes %d / %d (keys up to %d)", d, dv, DL * 16);
@@ -167,10 +194,16 @@ LILY_API int lily_delta_rule(const void* qkv, int qkv_stride, int q_col, int k_c
     a.heads = heads; a.kv_heads = kv_heads; a.d = d; a.dv = dv; a.unit_eps = unit_eps; a.q_scale = q_scale;
     dim3 grid(requests, heads, (dv + DELTA_COLS - 1) / DELTA_COLS), block(DELTA_THREADS);
     const int rows = (d + DL - 1) / DL;
-#define GO(R)                                                                                             \
-    do {                                                                                                  \
-        if (dtype == kBF16) launch_pdl(delta_rule_kernel<__nv_bfloat16, R>, grid, block, 0, stream, a);   \
-        else launch_pdl(delta_rule_kernel<float, R>, grid, block, 0, stream, a);                          \
+    const bool ahead = tokens > requests;               // some request brings more than one token
+#define GO(R)                                                                                                         \
+    do {                                                                                                              \
+        if (dtype == kBF16) {                                                                                         \
+            if (ahead) launch_pdl(delta_rule_kernel<__nv_bfloat16, R, true>, grid, block, 0, stream, a);              \
+            else launch_pdl(delta_rule_kernel<__nv_bfloat16, R, false>, grid, block, 0, stream, a);                   \
+        } else {                                                                                                      \
+            if (ahead) launch_pdl(delta_rule_kernel<float, R, true>, grid, block, 0, stream, a);                      \
+            else launch_pdl(delta_rule_kernel<float, R, false>, grid, block, 0, stream, a);                           \
+        }                                                                                                             \
     } while (0)
     if (rows <= 1) GO(1);
     else if (rows <= 2) GO(2);

@@ -319,7 +319,7 @@ __global__ void silu_mul_kernel(const Summed<IN> gate_up, T* __restrict__ out, i
 // and stores, eight outputs a thread and turn, the exponential and the quotient in their fast forms (as the fused
 // gate/up kernels compute them; the result is rounded to bfloat16 either way).  2,048 x 12,288 outputs: 44 -> 25 us, 0.92 of HBM.
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out, int inter,
-                                       int block, size_t total, int act) {
+                                       int block, size_t total, int act, float limit, float alpha) {
     pdl_enter_small();
     const size_t step = (size_t)gridDim.x * blockDim.x * 8;
     for (size_t idx = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8; idx < total; idx += step) {
@@ -333,10 +333,14 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up
         __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
-            // act(g) = g * sigmoid(t): t = g for SiLU, 2 sqrt(2/pi) (g + 0.044715 g^3) for the tanh form of GELU
-            const float tx = act == 0 ? g.x : 1.5957691216057308f * (g.x + 0.044715f * g.x * g.x * g.x);
-            const float ty = act == 0 ? g.y : 1.5957691216057308f * (g.y + 0.044715f * g.y * g.y * g.y);
+            float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
+            if (act == 2) {                    // the clamped form: g' sigmoid(alpha g') (u' + 1)
+                g = make_float2(fminf(g.x, limit), fminf(g.y, limit));
+                u = make_float2(fminf(fmaxf(u.x, -limit), limit) + 1.f, fminf(fmaxf(u.y, -limit), limit) + 1.f);
+            }
+            // act(g) = g * sigmoid(t): t = g for SiLU, 2 sqrt(2/pi) (g + 0.044715 g^3) for the tanh form of GELU, alpha g for the clamped form
+            const float tx = act == 0 ? g.x : (act == 2 ? alpha * g.x : 1.5957691216057308f * (g.x + 0.044715f * g.x * g.x * g.x));
+            const float ty = act == 0 ? g.y : (act == 2 ? alpha * g.y : 1.5957691216057308f * (g.y + 0.044715f * g.y * g.y * g.y));
             o2[j] = __floats2bfloat162_rn(__fdividef(g.x, 1.f + __expf(-tx)) * u.x, __fdividef(g.y, 1.f + __expf(-ty)) * u.y);
         }
         *reinterpret_cast<uint4*>(out + idx) = ov;
@@ -755,10 +759,10 @@ LILY_API int lily_silu_mul(const void* gate_up, void* out, int tokens, int inter
 #define GO(T, IN, V) launch_pdl(silu_mul_kernel<T, IN, V>, dim3(blocks), dim3(256), 0, stream, Summed<IN>{(const IN*)gate_up, splits, stride}, (T*)out, inter, block, total, act, limit, alpha)
     LILY_REQUIRE(act >= 0 && act <= 2, "silu_mul: activation %d (0: SiLU, 1: GELU, tanh form, 2: clamped)", act);
     LILY_REQUIRE(act != 2 || limit > 0.f, "silu_mul: the clamped form needs a positive limit");
-    if (act != 2 && act_dtype == kBF16 && in_dtype == kBF16 && splits == 1 && block % 8 == 0 && aligned16(gate_up) && aligned16(out)) {
+    if (act_dtype == kBF16 && in_dtype == kBF16 && splits == 1 && block % 8 == 0 && aligned16(gate_up) && aligned16(out)) {
         const size_t work8 = total / 8;
         const int blocks8 = (int)((work8 + 255) / 256 < (size_t)sm_count() * 16 ? (work8 + 255) / 256 : (size_t)sm_count() * 16);
-        launch_pdl(silu_mul_bf16x8_kernel, dim3(blocks8), dim3(256), 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, total, act);
+        launch_pdl(silu_mul_bf16x8_kernel, dim3(blocks8), dim3(256), 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, block, total, act, limit, alpha);
     } else if (act_dtype == kBF16 && in_dtype == kBF16) { if (vec) GO(__nv_bfloat16, __nv_bfloat16, 4); else GO(__nv_bfloat16, __nv_bfloat16, 1); }
     else if (act_dtype == kBF16) { if (vec) GO(__nv_bfloat16, float, 4); else GO(__nv_bfloat16, float, 1); }
     else { if (vec) GO(float, float, 4); else GO(float, float, 1); }

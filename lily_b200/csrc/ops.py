@@ -38,9 +38,9 @@ _SIGNATURES = {
     "lily_attention_prefill_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _i, _i, _vp],
     "lily_attention_decode_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _i, _i, _vp],
     "lily_attention_combine": [_vp, _vp, _i, _i, _i, _i, _i, _vp],
-    "lily_attention_prefill_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _i, _vp],
+    "lily_attention_prefill_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _i, _i, _i, _vp],
     "lily_attention_prefill_tc": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _f, _i, _vp],
-    "lily_attention_decode_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _vp],
+    "lily_attention_decode_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _i, _i, _vp],
     "lily_attention_decode_mma_fused": [_vp, _i, _sz, _i, _vp, _vp, _i, _f, _vp, _vp, _i, _i, _vp, _vp, _vp, _i, _vp, _vp,
                                         _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _vp],
     "lily_sigmoid_gate": [_vp, _i, _vp, _i, _i, _sz, _sz, _vp],
@@ -48,9 +48,9 @@ _SIGNATURES = {
     "lily_causal_conv_silu": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _sz, _sz, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _vp],
     "lily_causal_conv": [_vp, _i, _i, _i, _i, _vp, _vp, _vp, _sz, _sz, _vp, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _vp],
     "lily_add_normed_rmsnorm": [_vp, _vp, _i, _i, _sz, _vp, _f, _f, _vp, _i, _vp, _i, _vp, _i, _i, _f, _i, _i, _vp],
-    "lily_head_mix": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
-    "lily_delta_rule": [_vp, _i, _i, _i, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _sz, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _f, _i, _vp],
-    "lily_selective_scan": [_vp, _vp, _i, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _vp, _sz, _vp, _vp, _vp, _i, _i, _i, _i, _vp],
+    "lily_head_mix": [_vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "lily_delta_rule": [_vp, _i, _i, _i, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _sz, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _i, _vp],
+    "lily_selective_scan": [_vp, _vp, _i, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _vp, _sz, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "lily_activation": [_vp, _i, _i, _sz, _vp, _i, _sz, _i, _vp],
     "lily_diff_prepare": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp],
     "lily_diff_combine": [_vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _f, _f, _i, _vp],
@@ -589,6 +589,8 @@ def prefill_tile_rows(dtype: torch.dtype = torch.float32, d: int = 0, page_size:
     lib = library()
     if values_in_keys and heads and latent_tensor_cores(dtype, d, dv, softcap=softcap):
         return int(lib.lily_latent_attention_mma_tile_tokens(int(heads)))
+    if (sink or all_values) and sink_on_tensor_cores(dtype, d, dv, values_in_keys, softcap):
+        return int(lib.lily_attention_prefill_mma_rows())
     same = (dv is None or dv == d) and not values_in_keys and not sink and not all_values      # those run on CUDA cores
     if same and uses_tcgen05_attention(dtype, d, page_size, new_tokens):
         return int(lib.lily_attention_prefill_tc_rows())
@@ -619,8 +621,23 @@ def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torc
     kernel: the tcgen05 kernel takes tiles of its own size, the others theirs.  ``heads_per_block``
     (tcgen05 only) 1 or 2 picks between its one-head and its two-head form; 0 lets the launcher choose."""
     _dev(q, kv_layer, block_table, cu_seqlens, prefix_lens, tile_req, tile_start, out)
-    if q.dtype != kv_layer.dtype or out.dtype != (torch.float32 if all_values else q.dtype):
-        raise KernelError("attention: q, cache and out must share a dtype (sums over all kv heads' values are float32)")
+    planes = all_values and out.dim() == 3            # one launch of the mma.sync kernel a kv head (``all_values_sums``)
+    if q.dtype != kv_layer.dtype or out.dtype != (torch.float32 if all_values and not planes else q.dtype):
+        raise KernelError("attention: q, cache and out must share a dtype (sums over all kv heads' values on CUDA cores are float32)")
+    if (sink or all_values) and sink_on_tensor_cores(q.dtype, d, dv, values_in_keys, softcap) and (planes or not all_values):
+        if (tile_rows or 0) not in (0, int(library().lily_attention_prefill_mma_rows())):
+            raise KernelError(f"attention_prefill: the sink runs in tiles of {library().lily_attention_prefill_mma_rows()} rows")
+        if planes and tuple(out.shape) != (nkv, q.shape[0], nq * d):
+            raise KernelError(f"attention_prefill: planes of sums are [{nkv}, tokens, nq * d]")
+        for shift in range(nkv if planes else 1):
+            _call("lily_attention_prefill_mma", _p(q), _p(kv_layer), out[shift].data_ptr() if planes else _p(out),
+                  _i32(block_table, "block_table"), block_table.shape[-1], _i32(cu_seqlens, "cu_seqlens"),
+                  _i32(prefix_lens, "prefix_lens"), _i32(tile_req, "tile_req"), _i32(tile_start, "tile_start"), tile_req.numel(),
+                  nq, nkv, d, page_size, int(window or 0), float(scale), float(softcap or 0.0),
+                  int(keep_first or 0) if window else 0, int(bool(sink)), shift, _stream())
+        return
+    if planes:
+        raise KernelError("attention_prefill: planes of sums are the mma.sync kernels' (bfloat16, one head size for keys and values)")
     common = (_p(q), _p(kv_layer), _p(out), _i32(block_table, "block_table"), block_table.shape[-1],
               _i32(cu_seqlens, "cu_seqlens"), _i32(prefix_lens, "prefix_lens"), _i32(tile_req, "tile_req"),
               _i32(tile_start, "tile_start"), tile_req.numel(), nq, nkv, d, page_size, int(window or 0), float(scale))
@@ -647,9 +664,30 @@ def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torc
             raise KernelError("attention_prefill: the tcgen05 kernel takes contiguous q, out and cache")
         _call("lily_attention_prefill_tc", *common, q.shape[0], kv_layer.shape[0], int(heads_per_block), cap, keep_first, _stream())
     elif tensor_cores:
-        _call("lily_attention_prefill_mma", *common, cap, keep_first, _stream())
+        _call("lily_attention_prefill_mma", *common, cap, keep_first, 0, 0, _stream())
     else:
         _call("lily_attention_prefill_simt", *common, _dt(q), cap, -dv if values_in_keys else dv, keep_first, flags, _stream())
+
+
+_SIMT_SINK = os.environ.get("LILY_B200_SINK_ATTENTION", "") == "simt"
+
+
+def sink_on_tensor_cores(dtype: torch.dtype, d: int, dv: Optional[int] = None, values_in_keys: bool = False,
+                         softcap: Optional[float] = None) -> bool:
+    """Whether attention with a sink (and, in one launch a kv head, with the values of all kv heads) runs on the mma.sync
+    kernels: bfloat16, keys and values of one head size that those kernels take; else the CUDA-core kernels."""
+    return (not _SIMT_SINK and not values_in_keys and int(dv or d) == d and uses_tensor_cores(dtype, d))
+
+
+def all_values_sums(dtype: torch.dtype, tokens: int, nq: int, nkv: int, d: int, dv: Optional[int], device) -> torch.Tensor:
+    """The tensor that ``attention_prefill`` / ``attention_decode`` with ``all_values`` fill and ``head_mix`` reads.  On
+    the CUDA-core kernels float32 [tokens, nq * nkv * dv]: a query head's row holds its weights' sums over every kv
+    head's values.  On the mma.sync kernels ``nkv`` planes [nkv, tokens, nq * dv] in ``dtype``: plane s holds, for a
+    query head of kv head g, the sums over the values of kv head (g + s) % nkv (one launch a plane)."""
+    dv = int(dv or d)
+    if sink_on_tensor_cores(dtype, d, dv):
+        return torch.empty((nkv, tokens, nq * dv), dtype=dtype, device=device)
+    return torch.empty((tokens, nq * nkv * dv), dtype=torch.float32, device=device)
 
 
 def _attention_flags(sink: bool, all_values: bool, values_in_keys: bool, nkv: int, dv: int, out: torch.Tensor, rows: int) -> int:
@@ -657,7 +695,7 @@ def _attention_flags(sink: bool, all_values: bool, values_in_keys: bool, nkv: in
     if all_values:
         if values_in_keys:
             raise KernelError("attention: values that are columns of the key rows belong to one shared head")
-        if out.dtype != torch.float32 or out.numel() != rows * nkv * dv:
+        if out.dim() == 2 and (out.dtype != torch.float32 or out.numel() != rows * nkv * dv):
             raise KernelError(f"attention: sums over all kv heads' values are float32 [rows, nq * {nkv} * {dv}]")
     return (1 if sink else 0) | (6 if all_values else 0)
 
@@ -683,12 +721,16 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
     kernel only): the key/value tiles a block holds, 0 for the default (``DecodePlan.stages``)."""
     _dev(q, kv_layer, block_table, seq_lens, out, scratch)
     requests = q.shape[0]
-    if q.dtype != kv_layer.dtype or out.dtype != (torch.float32 if all_values else q.dtype):
-        raise KernelError("attention: q, cache and out must share a dtype (sums over all kv heads' values are float32)")
+    planes = all_values and out.dim() == 3
+    if q.dtype != kv_layer.dtype or out.dtype != (torch.float32 if all_values and not planes else q.dtype):
+        raise KernelError("attention: q, cache and out must share a dtype (sums over all kv heads' values on CUDA cores are float32)")
     dv = int(dv or d)
     cap = float(softcap or 0.0)
     flags = _attention_flags(sink, all_values, values_in_keys, nkv, dv, out, requests * nq)
-    need = decode_scratch_floats(requests, nq, nkv * dv if all_values else dv, splits)
+    on_tc = bool(flags) and sink_on_tensor_cores(q.dtype, d, dv, values_in_keys, softcap) and (planes or not all_values)
+    if planes and not on_tc:
+        raise KernelError("attention_decode: planes of sums are the mma.sync kernels' (bfloat16, one head size for keys and values)")
+    need = decode_scratch_floats(requests, nq, dv if on_tc else (nkv * dv if all_values else dv), splits)
     if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
         raise KernelError(f"attention_decode: scratch of {need} float32 needed")
     common = (_p(q), _p(kv_layer), _p(out), _i32(block_table, "block_table"), block_table.shape[-1],
@@ -700,8 +742,16 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
               int(window or 0), float(scale), _stream())
         if splits > 1:
             _call("lily_attention_combine", _p(scratch), _p(out), requests, nq, dv, splits, _dt(q), _stream())
+    elif on_tc:
+        for shift in range(nkv if planes else 1):
+            _call("lily_attention_decode_mma", _p(q), _p(kv_layer), out[shift].data_ptr() if planes else _p(out),
+                  _i32(block_table, "block_table"), block_table.shape[-1], _i32(seq_lens, "seq_lens"), _p(scratch), requests, splits,
+                  nq, nkv, d, page_size, int(window or 0), float(scale), int(stages), cap, int(keep_first or 0) if window else 0,
+                  int(bool(sink)), shift, _stream())
+            if splits > 1 and (stages or requests * nkv * -(-(nq // nkv) // 16) > decode_clusters(d, splits, nq // nkv)):
+                launches["count"] += 1
     elif dv == d and not values_in_keys and not flags and uses_tensor_cores(q.dtype, d):
-        _call("lily_attention_decode_mma", *common, int(stages), cap, int(keep_first or 0) if window else 0, _stream())   # merges the splits itself (cluster, or combine behind)
+        _call("lily_attention_decode_mma", *common, int(stages), cap, int(keep_first or 0) if window else 0, 0, 0, _stream())   # merges the splits itself (cluster, or combine behind)
         if splits > 1 and (stages or requests * nkv * -(-(nq // nkv) // 16) > decode_clusters(d, splits, nq // nkv)):
             launches["count"] += 1                                   # the combine kernel, launched inside
     else:
@@ -1576,11 +1626,13 @@ def head_mix(sums: torch.Tensor, mix: torch.Tensor, nq: int, nkv: int, dv: int, 
     head's attention weights summed over the values of every kv head (``attention_*`` with ``all_values``), ``mix``
     float32 [nq, nq]; returns [tokens, nq * dv], each head over its own kv head's values with the mixed weights."""
     _dev(sums, mix)
-    tokens = sums.shape[0]
-    if sums.dtype != torch.float32 or mix.dtype != torch.float32 or sums.shape[1] != nq * nkv * dv or tuple(mix.shape) != (nq, nq):
-        raise KernelError("head_mix: float32 sums [tokens, nq * nkv * dv] and a float32 matrix [nq, nq]")
+    planes = sums.dim() == 3                   # [nkv, tokens, nq * dv]: plane s of a head of kv head g over kv head (g + s) % nkv
+    tokens = sums.shape[-2]
+    if mix.dtype != torch.float32 or tuple(mix.shape) != (nq, nq) or \
+            (tuple(sums.shape) != (nkv, tokens, nq * dv) if planes else (sums.dtype != torch.float32 or sums.shape[1] != nq * nkv * dv)):
+        raise KernelError("head_mix: float32 sums [tokens, nq * nkv * dv] or planes [nkv, tokens, nq * dv], and a float32 matrix [nq, nq]")
     out = torch.empty((tokens, nq * dv), dtype=out_dtype, device=sums.device)
-    _call("lily_head_mix", _p(sums), _p(mix), _p(out), tokens, nq, nkv, dv, _dt(out), _stream())
+    _call("lily_head_mix", _p(sums), _dt(sums), int(planes), _p(mix), _p(out), tokens, nq, nkv, dv, _dt(out), _stream())
     return out
 
 
@@ -1607,7 +1659,7 @@ def delta_rule(qkv: torch.Tensor, proj: torch.Tensor, b_col: int, a_col: int, a_
     y = torch.empty((n, heads * dv), dtype=torch.float32, device=qkv.device)
     _call("lily_delta_rule", _p(qkv), qkv.shape[1], 0, kv_heads * d, 2 * kv_heads * d, _p(proj), proj.shape[1], int(b_col),
           int(a_col), _p(a_log), _p(dt_bias), _p(state), state.shape[1], _p(y), _i32(cu_seqlens, "cu_seqlens"),
-          _i32(slots, "slots"), int(requests), heads, kv_heads, d, dv, float(unit_eps), float(q_scale), _dt(qkv), _stream())
+          _i32(slots, "slots"), int(requests), n, heads, kv_heads, d, dv, float(unit_eps), float(q_scale), _dt(qkv), _stream())
     return y
 
 
@@ -1634,5 +1686,5 @@ def selective_scan(x: torch.Tensor, low: torch.Tensor, b_col: int, step: torch.T
     out = torch.empty((tokens, inner), dtype=x.dtype, device=x.device)
     _call("lily_selective_scan", _p(x), _p(low), low.shape[1], int(b_col), int(b_col) + n, _p(step), _p(proj), proj.shape[1],
           int(z_col), _p(a), _p(d_skip), _p(state), state.shape[1], _p(out), _i32(cu_seqlens, "cu_seqlens"),
-          _i32(slots, "slots"), int(requests), inner, n, _dt(x), _stream())
+          _i32(slots, "slots"), int(requests), tokens, inner, n, _dt(x), _stream())
     return out

@@ -7,7 +7,8 @@
 //     y_t[c]  =  sum_n S[c][n] C_t[n] + D[c] x_t[c],        out_t[c] = y_t[c] * silu(z_t[c])
 //
 // SL lanes share a channel and hold NR state entries each; a block owns SCAN_CHANNELS channels of one request and
-// walks the request's new tokens in order; a token's B and C are staged once for all of the block's channels.  The
+// walks the request's new tokens in order; a token's B and C are staged once for all of the block's channels, and the
+// next tile's inputs are loaded into registers while the current one is worked on.  The
 // step size, the decay, the state and the sums are float32 whatever the activation dtype.  State row of a slot:
 // [inner][state] (state fastest) at the row's start.
 #include "common.cuh"
@@ -37,7 +38,9 @@ struct SelectiveArgs {
 };
 
 // grid (requests, ceil(inner / SCAN_CHANNELS)), block SCAN_THREADS; n_state <= SL * NR
-template <typename T, int NR>
+// AHEAD: a tile's inputs are loaded one tile ahead (portions of prompts); without it they are loaded when their turn
+// comes, which keeps fewer registers alive (steps in which every request brings one token).
+template <typename T, int NR, bool AHEAD>
 __global__ void __launch_bounds__(SCAN_THREADS) selective_scan_kernel(const SelectiveArgs a) {
     constexpr int SP = SL * NR;
     __shared__ float Bs[SCAN_TOKENS][SP], Cs[SCAN_TOKENS][SP];
@@ -65,25 +68,51 @@ __global__ void __launch_bounds__(SCAN_THREADS) selective_scan_kernel(const Sele
     const T* z = (const T*)a.z;
     T* out = (T*)a.out;
 
+    // A tile's inputs are asked for into registers one tile ahead, so that they travel while the tile before is worked on.
+    constexpr int PER = SCAN_TOKENS * SP / SCAN_THREADS;                    // B (and C) entries a thread stages: NR
+    constexpr int CPER = SCAN_TOKENS * SCAN_CHANNELS / SCAN_THREADS;        // step, x and z entries a thread stages: 2
+    float rB[PER], rC[PER], rs[CPER], rx[CPER], rz[CPER];
+    auto fetch = [&](int t0) {
+        const int n = min(SCAN_TOKENS, len - t0);
+#pragma unroll
+        for (int it = 0; it < PER; ++it) {
+            const int e = it * SCAN_THREADS + threadIdx.x, t = e / SP, i = e % SP;
+            const bool ok = t < n && i < ns;
+            const T* row = low + (size_t)(tok0 + t0 + (ok ? t : 0)) * a.low_stride + (ok ? i : 0);
+            rB[it] = ok ? to_float(row[a.b_col]) : 0.f;
+            rC[it] = ok ? to_float(row[a.c_col]) : 0.f;
+        }
+#pragma unroll
+        for (int it = 0; it < CPER; ++it) {
+            const int e = it * SCAN_THREADS + threadIdx.x, t = e / SCAN_CHANNELS, c = e % SCAN_CHANNELS;
+            const bool ok = t < n && ch0 + c < inner;
+            const size_t tok = tok0 + t0 + (ok ? t : 0);
+            rs[it] = ok ? a.step[tok * inner + ch0 + c] : 0.f;
+            rx[it] = ok ? to_float(x[tok * inner + ch0 + c]) : 0.f;
+            rz[it] = ok ? to_float(z[tok * a.z_stride + a.z_col + ch0 + c]) : 0.f;
+        }
+    };
+    if (AHEAD) fetch(0);
+
     for (int t0 = 0; t0 < len; t0 += SCAN_TOKENS) {
         const int n = min(SCAN_TOKENS, len - t0);
+        if (!AHEAD) fetch(t0);
         __syncthreads();
-        for (int e = threadIdx.x; e < n * SP; e += SCAN_THREADS) {
-            const int t = e / SP, i = e % SP;
-            const T* row = low + (size_t)(tok0 + t0 + t) * a.low_stride + i;
-            Bs[t][i] = i < ns ? to_float(row[a.b_col]) : 0.f;
-            Cs[t][i] = i < ns ? to_float(row[a.c_col]) : 0.f;
+#pragma unroll
+        for (int it = 0; it < PER; ++it) {
+            const int e = it * SCAN_THREADS + threadIdx.x;
+            Bs[e / SP][e % SP] = rB[it];
+            Cs[e / SP][e % SP] = rC[it];
         }
-        for (int e = threadIdx.x; e < n * SCAN_CHANNELS; e += SCAN_THREADS) {
-            const int t = e / SCAN_CHANNELS, c = e % SCAN_CHANNELS;
-            const size_t tok = tok0 + t0 + t;
-            const bool ok = ch0 + c < inner;
-            const float s = ok ? a.step[tok * inner + ch0 + c] : 0.f;
-            dts[t][c] = s > 20.f ? s : log1pf(expf(s));
-            xs[t][c] = ok ? to_float(x[tok * inner + ch0 + c]) : 0.f;
-            zs[t][c] = ok ? to_float(z[tok * a.z_stride + a.z_col + ch0 + c]) : 0.f;
+#pragma unroll
+        for (int it = 0; it < CPER; ++it) {
+            const int e = it * SCAN_THREADS + threadIdx.x, t = e / SCAN_CHANNELS, c = e % SCAN_CHANNELS;
+            dts[t][c] = rs[it] > 20.f ? rs[it] : log1pf(expf(rs[it]));
+            xs[t][c] = rx[it];
+            zs[t][c] = rz[it];
         }
         __syncthreads();
+        if (AHEAD && t0 + SCAN_TOKENS < len) fetch(t0 + SCAN_TOKENS);
         for (int t = 0; t < n; ++t) {
             const float dt = dts[t][cg], xv = xs[t][cg], dx = dt * xv;
             float acc = 0.f;
@@ -122,7 +151,7 @@ LILY_API int lily_selective_scan_max_state() { return SL * 32; }
 
 LILY_API int lily_selective_scan(const void* x, const void* low, int low_stride, int b_col, int c_col, const float* step,
                                  const void* z, int z_stride, int z_col, const float* A, const float* D, float* state,
-                                 size_t state_stride, void* out, const int* cu_seqlens, const int* slots, int requests,
+                                 size_t state_stride, void* out, const int* cu_seqlens, const int* slots, int requests, int tokens,
                                  int inner, int n_state, int dtype, cudaStream_t stream) {
     if (requests == 0) return 0;
     LILY_REQUIRE(inner > 0 && n_state > 0 && n_state <= SL * 32, "selective_scan: %d channels of %d state entries (up to %d)", inner, n_state, SL * 32);
@@ -134,10 +163,16 @@ LILY_API int lily_selective_scan(const void* x, const void* low, int low_stride,
     a.out = out; a.cu_seqlens = cu_seqlens; a.slots = slots; a.inner = inner; a.n_state = n_state;
     dim3 grid(requests, (inner + SCAN_CHANNELS - 1) / SCAN_CHANNELS), block(SCAN_THREADS);
     const int per = (n_state + SL - 1) / SL;
-#define GO(NR)                                                                                                 \
-    do {                                                                                                       \
-        if (dtype == kBF16) launch_pdl(selective_scan_kernel<__nv_bfloat16, NR>, grid, block, 0, stream, a);   \
-        else launch_pdl(selective_scan_kernel<float, NR>, grid, block, 0, stream, a);                          \
+    const bool ahead = tokens > requests;               // some request brings more than one token
+#define GO(NR)                                                                                                            \
+    do {                                                                                                                  \
+        if (dtype == kBF16) {                                                                                             \
+            if (ahead) launch_pdl(selective_scan_kernel<__nv_bfloat16, NR, true>, grid, block, 0, stream, a);             \
+            else launch_pdl(selective_scan_kernel<__nv_bfloat16, NR, false>, grid, block, 0, stream, a);                  \
+        } else {                                                                                                          \
+            if (ahead) launch_pdl(selective_scan_kernel<float, NR, true>, grid, block, 0, stream, a);                     \
+            else launch_pdl(selective_scan_kernel<float, NR, false>, grid, block, 0, stream, a);                          \
+        }                                                                                                                 \
     } while (0)
     if (per <= 1) GO(1);
     else if (per <= 2) GO(2);

@@ -217,9 +217,12 @@ class Attention(Mixer):
             sized = dict(sized, keep_first=int(s.keep_first))
         tiled = dict(sized)
         if s.sink or s.talk:
-            # options of the CUDA-core kernels; with mixed heads a query head's output row spans all kv heads' values
-            sized = dict(sized, cuda_cores=True, dv=s.num_kv_heads * s.value_dim if s.talk else s.value_dim)
             tiled = dict(tiled, sink=s.sink, all_values=s.talk)
+            if not ops.sink_on_tensor_cores(dtype, s.head_dim, s.value_dim):
+                # options of the CUDA-core kernels; with mixed heads a query head's output row spans all kv heads' values
+                sized = dict(sized, cuda_cores=True, dv=s.num_kv_heads * s.value_dim if s.talk else s.value_dim)
+            else:
+                sized = dict(sized, fusable=False)      # one launch a kv head of the mma.sync kernel, queries prepared ahead
 
         def make(b):
             nd = b.num_decode
@@ -285,11 +288,13 @@ class Attention(Mixer):
                                    batch.token_req, table, cache.data, s.num_heads, s.num_kv_heads, s.head_dim,
                                    rotary_dim, page, write_kv=write_cache, **sized, **values)
         if s.talk:
-            out = torch.empty((q.shape[0], s.num_heads * s.num_kv_heads * dv), dtype=torch.float32, device=q.device)
+            out = ops.all_values_sums(q.dtype, q.shape[0], s.num_heads, s.num_kv_heads, s.head_dim, dv, q.device)
         else:
             out = torch.empty((q.shape[0], s.num_heads * dv), dtype=q.dtype, device=q.device)
+        planes = out.dim() == 3                          # a plane a kv head (the mma.sync kernels) instead of wider rows
         if nd:
-            ops.attention_decode(q[:nd], cache.data, table, batch.seq_lens, out[:nd], scratch, dec.splits,
+            # (the one-token requests' rows are the first of every plane)
+            ops.attention_decode(q[:nd], cache.data, table, batch.seq_lens, out if planes else out[:nd], scratch, dec.splits,
                                  s.num_heads, s.num_kv_heads, s.head_dim, page, self.scale, s.window, stages=dec.stages,
                                  **capped, **sized, **kept)
         if batch.num_requests > nd:

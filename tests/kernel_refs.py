@@ -681,6 +681,14 @@ def diff_combine(maps_out, proj, gate_col, heads, dv, maps, lam, out_scale, eps)
 
 # ---------------------------------------------------------------------------- mixed heads, delta rule, selective scan
 
+def sink_on_tensor_cores(dtype, d, dv=None, values_in_keys=False, softcap=None):
+    return False
+
+
+def all_values_sums(dtype, tokens, nq, nkv, d, dv, device):
+    return torch.empty((tokens, nq * nkv * (dv or d)), dtype=torch.float32, device=device)
+
+
 def head_mix(sums, mix, nq, nkv, dv, out_dtype):
     """out[t, h] = sum_g mix[h, g] sums[t, g, kv(h)]; sums float32 [tokens, nq * nkv * dv]."""
     n = sums.shape[0]

@@ -138,6 +138,7 @@ __global__ void __launch_bounds__(DELTA_THREADS) delta_rule_kernel(const DeltaAr
             }
         }
         __syncthreads();
+#pragma unroll 2
         for (int t = 0; t < n; ++t) {
             float sk = 0.f, sq = 0.f, kq = 0.f, kk[R];
 #pragma unroll

@@ -269,7 +269,7 @@ template <int WARPS, int STAGES, bool XSMEM, int KT>
 __global__ void __launch_bounds__(WARPS * 32)
 skinny_swiglu_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                      __nv_bfloat16* __restrict__ out, float* __restrict__ scratch, int* __restrict__ counters,
-                     int M, int I, int K, int run, int row_blocks, int max_seg, int x_slots, int act) {
+                     int M, int I, int K, int run, int row_blocks, int max_seg, int x_slots, int act, float limit, float alpha) {
     static_assert(!XSMEM || KT == 64, "x is staged in shared memory in blocks of 64 k");
     constexpr int PIECES = KT / 8, PITCH = KT * 2, TILE = 16 * PITCH, COPIES = KT / 16, OUTS = 8 * WARPS;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -419,9 +419,13 @@ skinny_swiglu_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int tok = 2 * c + e;
-                    const float gate = acc[e], up = acc[2 + e];
-                    // act(g) = g * sigmoid(t): t = g for SiLU; t = 2 sqrt(2/pi) (g + 0.044715 g^3) for the tanh form of GELU
-                    const float t = act == 0 ? gate : 1.5957691216057308f * (gate + 0.044715f * gate * gate * gate);
+                    float gate = acc[e], up = acc[2 + e];
+                    if (act == 2) {                  // the clamped form: g' sigmoid(alpha g') (u' + 1)
+                        gate = fminf(gate, limit);
+                        up = fminf(fmaxf(up, -limit), limit) + 1.f;
+                    }
+                    // act(g) = g * sigmoid(t): t = g for SiLU; t = 2 sqrt(2/pi) (g + 0.044715 g^3) for the tanh form of GELU; alpha g for the clamped form
+                    const float t = act == 0 ? gate : (act == 2 ? alpha * gate : 1.5957691216057308f * (gate + 0.044715f * gate * gate * gate));
                     if (o < I && tok < M) out[(size_t)tok * I + o] = __float2bfloat16_rn(gate / (1.f + __expf(-t)) * up);
                 }
             }
@@ -473,7 +477,8 @@ static SwigluPlan swiglu_plan(int M, int I, int K, int run) {
 
 template <bool XSMEM>
 static int launch_swiglu(const SwigluPlan& p, const __nv_bfloat16* x, const __nv_bfloat16* w, __nv_bfloat16* out,
-                         float* scratch, int* counters, int M, int I, int K, int run, int act, cudaStream_t stream) {
+                         float* scratch, int* counters, int M, int I, int K, int run, int act, float limit, float alpha,
+                         cudaStream_t stream) {
     auto kern = skinny_swiglu_kernel<SWIGLU_WARPS, SWIGLU_STAGES, XSMEM, SWIGLU_KT>;
     static size_t granted = 48 * 1024;
     if (p.smem > granted) {
@@ -485,7 +490,7 @@ static int launch_swiglu(const SwigluPlan& p, const __nv_bfloat16* x, const __nv
         granted = p.smem;
     }
     launch_pdl(kern, dim3(p.grid), dim3(SWIGLU_WARPS * 32), p.smem, stream, x, w, out, scratch, counters, M, I, K, run,
-               p.row_blocks, p.max_seg, p.x_slots, act);
+               p.row_blocks, p.max_seg, p.x_slots, act, limit, alpha);
     return 0;
 }
 
@@ -556,8 +561,8 @@ LILY_API int lily_skinny_swiglu_need(int M, int I, int K, int run, size_t* scrat
 // out [M, I] bfloat16 = silu(x . gate^T) * (x . up^T); w [2 I, K] holds runs of `run` gate rows and the `run` up
 // rows of the same outputs (run == I: all gate rows, then all up rows).
 LILY_API int lily_skinny_swiglu(const void* x, const void* w, void* out, float* scratch, int* counters, int M, int I,
-                                int K, int run, int act, cudaStream_t stream) {
-    LILY_REQUIRE(act == 0 || act == 1, "skinny_swiglu: activation %d (0: SiLU, 1: GELU, tanh form)", act);
+                                int K, int run, int act, float limit, float alpha, cudaStream_t stream) {
+    LILY_REQUIRE(act >= 0 && act <= 2 && (act != 2 || limit > 0.f), "skinny_swiglu: activation %d (0: SiLU, 1: GELU, tanh form, 2: clamped with a positive limit)", act);
     if (M == 0 || I == 0) return 0;
     const skinny::SwigluPlan p = skinny::swiglu_plan(M, I, K, run);
     LILY_REQUIRE(p.grid > 0, "skinny_swiglu: does not take M=%d I=%d K=%d run=%d (1 to 8 tokens, K a multiple of 64, "
@@ -567,8 +572,8 @@ LILY_API int lily_skinny_swiglu(const void* x, const void* w, void* out, float* 
     const __nv_bfloat16* xp = (const __nv_bfloat16*)x;
     const __nv_bfloat16* wp = (const __nv_bfloat16*)w;
     __nv_bfloat16* op = (__nv_bfloat16*)out;
-    const int rc = p.xsmem ? skinny::launch_swiglu<true>(p, xp, wp, op, scratch, counters, M, I, K, run, act, stream)
-                           : skinny::launch_swiglu<false>(p, xp, wp, op, scratch, counters, M, I, K, run, act, stream);
+    const int rc = p.xsmem ? skinny::launch_swiglu<true>(p, xp, wp, op, scratch, counters, M, I, K, run, act, limit, alpha, stream)
+                           : skinny::launch_swiglu<false>(p, xp, wp, op, scratch, counters, M, I, K, run, act, limit, alpha, stream);
     if (rc) return rc;
     LILY_CHECK_LAUNCH("skinny_swiglu");
     return 0;

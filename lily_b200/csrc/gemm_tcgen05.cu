@@ -46,7 +46,8 @@ constexpr uint32_t SPIN_LIMIT = 1u << 24;     // ~ a second of polling before a 
 __device__ int g_status = 0;                  // 0 ok; else (code << 16 | block) of the first wait that gave up
 
 enum Epilogue : int { kPlain = 0, kSiluMul = 1, kGeluMul = 2,       // 2: the tanh form of GELU in place of SiLU
-                      kActSilu = 3, kActGelu = 4, kActRelu2 = 5 };  // the plain product with an activation on every output
+                      kActSilu = 3, kActGelu = 4, kActRelu2 = 5,    // the plain product with an activation on every output
+                      kClampMul = 6 };   // gate * up in the clamped form: g' sigmoid(p1 g') (u' + 1), g' = min(g, p0), u' = clamp(u, -p0, p0)
 
 // The activation of the plain epilogues 3 to 5 (SiLU, the tanh form of GELU, the square of max(., 0)); else the identity.
 template <int EPI>
@@ -125,8 +126,8 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
 template <int EPI>
 __device__ __forceinline__ void epilogue_tile(uint32_t tbase, __nv_bfloat16* __restrict__ C,
                                               const __nv_bfloat16* __restrict__ bias, int row, int m_ok, int n0, int N,
-                                              int ldc, int half) {
-    if (EPI == kPlain || EPI >= kActSilu) {
+                                              int ldc, int half, float p0, float p1) {
+    if (EPI == kPlain || (EPI >= kActSilu && EPI <= kActRelu2)) {
 #pragma unroll 1
         for (int cc = half * (BN / 64); cc < (half + 1) * (BN / 64); ++cc) {   // this warp's half of the columns
             uint32_t r[32];
@@ -164,10 +165,14 @@ __device__ __forceinline__ void epilogue_tile(uint32_t tbase, __nv_bfloat16* __r
                 float f[32];
 #pragma unroll
                 for (int e = 0; e < 32; ++e) {
-                    const float gv = __uint_as_float(gte[e]);
-                    // act(g) = g * sigmoid(t): t = g for SiLU, 2 sqrt(2/pi) (g + 0.044715 g^3) for the tanh form of GELU
-                    const float t = EPI == kGeluMul ? 1.5957691216057308f * (gv + 0.044715f * gv * gv * gv) : gv;
-                    f[e] = __fdividef(gv, 1.f + __expf(-t)) * __uint_as_float(up[e]);
+                    float gv = __uint_as_float(gte[e]), uv = __uint_as_float(up[e]);
+                    if (EPI == kClampMul) {
+                        gv = fminf(gv, p0);
+                        uv = fminf(fmaxf(uv, -p0), p0) + 1.f;
+                    }
+                    // act(g) = g * sigmoid(t): t = g for SiLU, 2 sqrt(2/pi) (g + 0.044715 g^3) for the tanh form of GELU, p1 g for the clamped form
+                    const float t = EPI == kGeluMul ? 1.5957691216057308f * (gv + 0.044715f * gv * gv * gv) : (EPI == kClampMul ? p1 * gv : gv);
+                    f[e] = __fdividef(gv, 1.f + __expf(-t)) * uv;
                 }
                 if (col + 32 <= N / 2 && (ldc & 7) == 0) {
 #pragma unroll
@@ -185,7 +190,7 @@ __device__ __forceinline__ void epilogue_tile(uint32_t tbase, __nv_bfloat16* __r
 template <int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int ldc) {
+               __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int ldc, float p0, float p1) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     // the dynamic region is only guaranteed 16-byte alignment: round up to the 1024 the swizzle needs
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -278,7 +283,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (!mbar_wait(ready0 + 8 * acc, (local >> 1) & 1, abort_flag, 3)) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const int row = m0 + quarter * 32 + lane;
-            epilogue_tile<EPI>(tmem + acc * BN + ((uint32_t)(quarter * 32) << 16), C, bias, row, row < M, n0, N, ldc, (warp - 2) >> 2);
+            epilogue_tile<EPI>(tmem + acc * BN + ((uint32_t)(quarter * 32) << 16), C, bias, row, row < M, n0, N, ldc, (warp - 2) >> 2, p0, p1);
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(drained0 + 8 * acc);
@@ -348,7 +353,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_in_cluster) {
 template <int EPI>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int ldc) {
+                    __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ bias, int M, int N, int K, int ldc, float p0, float p1) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     __shared__ __align__(8) uint64_t bars[2 * PAIR_STAGES + 4];
@@ -443,7 +448,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if (!mbar_wait(ready0 + 8 * acc, (local >> 1) & 1, abort_flag, 3)) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const int row = m0 + quarter * 32 + lane;
-            epilogue_tile<EPI>(tmem + acc * BN + ((uint32_t)(quarter * 32) << 16), C, bias, row, row < M, n0, N, ldc, (warp - 2) >> 2);
+            epilogue_tile<EPI>(tmem + acc * BN + ((uint32_t)(quarter * 32) << 16), C, bias, row, row < M, n0, N, ldc, (warp - 2) >> 2, p0, p1);
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(in_block(drained0 + 8 * acc, 0));
@@ -503,7 +508,7 @@ static bool pair_enabled() {
 
 template <int EPI>
 static int launch(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldc,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, float p0 = 0.f, float p1 = 0.f) {
     const int sms = sm_count();
     // The pair form works on 256 rows at a time: an odd number of 128-row blocks costs it a whole block of padding,
     // which up to some 2,000 rows is more than the pair's better rate gives back (gate/up product of Qwen3-8B, pair /
@@ -540,7 +545,7 @@ static int launch(const void* A, const void* B, void* C, const void* bias, int M
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        cudaLaunchKernelEx(&cfg, kern, ma, mb, (__nv_bfloat16*)C, (const __nv_bfloat16*)bias, M, N, K, ldc);
+        cudaLaunchKernelEx(&cfg, kern, ma, mb, (__nv_bfloat16*)C, (const __nv_bfloat16*)bias, M, N, K, ldc, p0, p1);
         return 0;
     }
     CUtensorMap ma, mb;
@@ -559,7 +564,7 @@ static int launch(const void* A, const void* B, void* C, const void* bias, int M
     }
     const long tiles = (long)((N + BN - 1) / BN) * ((M + BM - 1) / BM);
     dim3 grid((unsigned)(tiles < sms ? tiles : sms));
-    kern<<<grid, THREADS, smem, stream>>>(ma, mb, (__nv_bfloat16*)C, (const __nv_bfloat16*)bias, M, N, K, ldc);
+    kern<<<grid, THREADS, smem, stream>>>(ma, mb, (__nv_bfloat16*)C, (const __nv_bfloat16*)bias, M, N, K, ldc, p0, p1);
     return 0;
 }
 
@@ -582,16 +587,19 @@ LILY_API int lily_gemm_tc_status() {
 // epilogue 0: C [M, N] = A . B^T (+ bias [N]).  epilogue 1: C [M, N / 2] = silu(gate) * up where the
 // rows of B alternate between 128 gate rows and the 128 up rows of the same outputs (N % 256 == 0); 2: the same with
 // the tanh form of GELU.  epilogues 3, 4, 5: C [M, N] = act(A . B^T (+ bias)), act = SiLU, GELU (tanh form), relu(.)^2.
+// epilogue 6: as 1 in the clamped form g' sigmoid(p1 g') (u' + 1) with g' = min(gate, p0), u' = clamp(up, -p0, p0).
 LILY_API int lily_gemm_tc(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldc,
-                          int epilogue, cudaStream_t stream) {
+                          int epilogue, float p0, float p1, cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
     LILY_REQUIRE(K > 0 && K % 8 == 0 && lda % 8 == 0 && lda >= K, "gemm_tc: K=%d, lda=%d must be multiples of 8", K, lda);
     LILY_REQUIRE(((uintptr_t)A % 16 == 0) && ((uintptr_t)B % 16 == 0) && ((uintptr_t)C % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
     int rc;
-    if (epilogue == tc::kSiluMul || epilogue == tc::kGeluMul) {
+    if (epilogue == tc::kSiluMul || epilogue == tc::kGeluMul || epilogue == tc::kClampMul) {
         LILY_REQUIRE(N % 256 == 0 && bias == nullptr && ldc >= N / 2, "gemm_tc: the gate*up epilogue takes N %% 256 == 0 and no bias");
-        rc = epilogue == tc::kSiluMul ? tc::launch<tc::kSiluMul>(A, B, C, nullptr, M, N, K, lda, ldc, stream)
-                                      : tc::launch<tc::kGeluMul>(A, B, C, nullptr, M, N, K, lda, ldc, stream);
+        LILY_REQUIRE(epilogue != tc::kClampMul || p0 > 0.f, "gemm_tc: the clamped gate needs a positive limit");
+        rc = epilogue == tc::kSiluMul   ? tc::launch<tc::kSiluMul>(A, B, C, nullptr, M, N, K, lda, ldc, stream)
+             : epilogue == tc::kGeluMul ? tc::launch<tc::kGeluMul>(A, B, C, nullptr, M, N, K, lda, ldc, stream)
+                                        : tc::launch<tc::kClampMul>(A, B, C, nullptr, M, N, K, lda, ldc, stream, p0, p1);
     } else {
         LILY_REQUIRE((epilogue == tc::kPlain || (epilogue >= tc::kActSilu && epilogue <= tc::kActRelu2)) && ldc >= N,
                      "gemm_tc: epilogue %d, ldc %d", epilogue, ldc);

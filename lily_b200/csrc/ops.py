@@ -28,11 +28,11 @@ _SIGNATURES = {
     "lily_scatter_tokens": [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp],
     "lily_add_rmsnorm": [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i, _i, _i, _i, _i, _sz, _vp],
     "lily_silu_mul": [_vp, _vp, _i, _i, _i, _i, _i, _i, _sz, _i, _f, _f, _vp],
-    "lily_gemm_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    "lily_gemm_tc": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _vp],
     "lily_qk_norm_rope_write": [_vp, _vp, _vp, _f, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i,
                                 _i, _i, _i, _i, _i, _sz, _i, _i, _f, _vp, _i, _vp],
     "lily_skinny_gemm": [_vp, _vp, _vp, _i, _i, _i, _i, _vp],
-    "lily_skinny_swiglu": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "lily_skinny_swiglu": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _f, _vp],
     "lily_cast": [_vp, _i, _vp, _i, _sz, _vp],
     "lily_gemm_fp32": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "lily_attention_prefill_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _i, _i, _vp],
@@ -429,11 +429,12 @@ def gemm_tc_takes(x: torch.Tensor, weight: torch.Tensor) -> bool:
 
 
 def gemm_tc(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
-            silu_mul_block: bool = False, activation: str = "silu", plain_activation: Optional[str] = None) -> torch.Tensor:
+            silu_mul_block: bool = False, activation: str = "silu", plain_activation: Optional[str] = None,
+            limit: float = 0.0, alpha: float = 1.0) -> torch.Tensor:
     """``x [M, K] . weight [N, K]^T`` in bfloat16 on the tcgen05 tensor cores (TMA-fed, accumulator
     in tensor memory).  With ``silu_mul_block`` the rows of ``weight`` alternate between 128 gate
     rows and the 128 up rows of the same outputs and the result is ``act(gate) * up`` [M, N / 2]
-    (``activation``: "silu" or "gelu_tanh").  ``plain_activation`` ("silu", "gelu_tanh", "relu2"): the plain product
+    (``activation``: "silu", "gelu_tanh", or "swish_clamped" with its ``limit`` and ``alpha``).  ``plain_activation`` ("silu", "gelu_tanh", "relu2"): the plain product
     with that activation on every output, applied to the float32 sums in the epilogue."""
     _dev(x, weight, bias)
     m, k = x.shape
@@ -442,8 +443,8 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] 
         raise KernelError(f"gemm_tc: x {tuple(x.shape)} {x.dtype} against weight {tuple(weight.shape)} {weight.dtype}")
     out = torch.empty((m, n // 2 if silu_mul_block else n), dtype=torch.bfloat16, device=x.device)
     _call("lily_gemm_tc", _p(x), _p(weight), _p(out), _p(bias), m, n, k, k, out.shape[1],
-          1 + ACTIVATIONS[activation] if silu_mul_block else (3 + PLAIN_ACTIVATIONS[plain_activation] if plain_activation else 0),
-          _stream())
+          (6 if activation == "swish_clamped" else 1 + ACTIVATIONS[activation]) if silu_mul_block
+          else (3 + PLAIN_ACTIVATIONS[plain_activation] if plain_activation else 0), float(limit), float(alpha), _stream())
     return out
 
 
@@ -507,7 +508,8 @@ _LIBRARY_SWIGLU = os.environ.get("LILY_B200_SWIGLU", "") == "library"
 
 
 def swiglu_skinny(x: torch.Tensor, gate_up: torch.Tensor, block: Optional[int], scratch: torch.Tensor,
-                  counters: torch.Tensor, out: Optional[torch.Tensor] = None, activation: str = "silu") -> torch.Tensor:
+                  counters: torch.Tensor, out: Optional[torch.Tensor] = None, activation: str = "silu",
+                  limit: float = 0.0, alpha: float = 1.0) -> torch.Tensor:
     """``act(x . gate^T) * (x . up^T)`` [tokens, I] for up to 8 tokens in one kernel that streams the fused
     gate/up matrix [2 I, K] once (rows in alternating runs of ``block`` gate and up rows; None: all gate, then all
     up).  ``scratch`` (float32) and ``counters`` (int32, zero before the first call; the kernel leaves them zero)
@@ -523,7 +525,7 @@ def swiglu_skinny(x: torch.Tensor, gate_up: torch.Tensor, block: Optional[int], 
     if out is None:
         out = torch.empty((m, inter), dtype=torch.bfloat16, device=x.device)
     _call("lily_skinny_swiglu", _p(x), _p(gate_up), _p(out), _p(scratch), _p(counters), m, inter, k, int(block or inter),
-          ACTIVATIONS[activation], _stream())
+          GATE_ACTIVATIONS[activation], float(limit), float(alpha), _stream())
     return out
 
 

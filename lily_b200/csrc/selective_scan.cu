@@ -113,7 +113,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) selective_scan_kernel(const Sele
         }
         __syncthreads();
         if (AHEAD && t0 + SCAN_TOKENS < len) fetch(t0 + SCAN_TOKENS);
-        for (int t = 0; t < n; ++t) {
+#pragma unroll 4
+        for (int t = 0; t < n; ++t) {                 // the exponentials and the lane sums of neighbouring tokens overlap
             const float dt = dts[t][cg], xv = xs[t][cg], dx = dt * xv;
             float acc = 0.f;
 #pragma unroll

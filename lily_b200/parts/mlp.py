@@ -57,8 +57,7 @@ class SwiGLU(FeedForward):
         gate = get(f"{p}.{name('gate')}")
         h = self.spec.hidden_size
         self.w_gate_up = torch.empty((2 * i, h), dtype=gate.dtype, device=gate.device)
-        # the clamped form has the stand-alone activation kernel only, which reads [all gate | all up]
-        self.block = b = None if self.spec.activation == "swish_clamped" else self.ctx.ops.gate_up_interleave(gate.dtype, i)
+        self.block = b = self.ctx.ops.gate_up_interleave(gate.dtype, i)
         if b:
             runs = self.w_gate_up.view(i // b, 2, b, h)
             runs[:, 0].copy_(gate.view(i // b, b, h))
@@ -73,11 +72,9 @@ class SwiGLU(FeedForward):
     def forward(self, x, batch):
         ops = self.ctx.ops
         product = ops.linear_auto                                # partial sums for a few tokens, else [M, N]
-        if self.spec.activation == "swish_clamped":
-            act = ops.silu_mul(product(x, self.w_gate_up), x.dtype, activation="swish_clamped", limit=self.spec.limit,
-                               alpha=self.spec.alpha)
-            return product(act, self.w_down)
         how = {} if self.spec.activation == "silu" else {"activation": self.spec.activation}
+        if self.spec.activation == "swish_clamped":
+            how.update(limit=self.spec.limit, alpha=self.spec.alpha)
         few = ops.swiglu_skinny_need(x.shape[0], self.spec.intermediate_size, self.spec.hidden_size, x.dtype, self.block)
         if few is not None and batch.workspace is not None:
             # a few tokens: one kernel streams the fused matrix and applies the activation and the product to its own sums

@@ -192,9 +192,9 @@ def swiglu_skinny_need(tokens, intermediate, hidden, dtype, block=None, whenever
     return (16, 4) if dtype == torch.bfloat16 and tokens <= 8 and hidden % 64 == 0 else None
 
 
-def swiglu_skinny(x, gate_up, block, scratch, counters, out=None, activation="silu"):
+def swiglu_skinny(x, gate_up, block, scratch, counters, out=None, activation="silu", limit=0.0, alpha=1.0):
     assert int(counters.abs().sum()) == 0           # the kernel finds them zero and leaves them zero
-    return silu_mul(linear(x, gate_up, out_dtype=torch.float32), x.dtype, block=block, activation=activation)
+    return silu_mul(linear(x, gate_up, out_dtype=torch.float32), x.dtype, block=block, activation=activation, limit=limit, alpha=alpha)
 
 
 def logits(x, head):
@@ -209,11 +209,11 @@ def gemm_tc_takes(x, weight):
     return x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
 
 
-def gemm_tc(x, weight, bias=None, silu_mul_block=False, activation="silu", plain_activation=None):
+def gemm_tc(x, weight, bias=None, silu_mul_block=False, activation="silu", plain_activation=None, limit=0.0, alpha=1.0):
     out = linear(x, weight, bias, out_dtype=torch.float32)
     if plain_activation:
         return _activate(out, plain_activation).to(x.dtype)
-    return silu_mul(out, x.dtype, block=128, activation=activation) if silu_mul_block else out.to(x.dtype)
+    return silu_mul(out, x.dtype, block=128, activation=activation, limit=limit, alpha=alpha) if silu_mul_block else out.to(x.dtype)
 
 
 def uses_tensor_cores(dtype, d):

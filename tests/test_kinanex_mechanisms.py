@@ -393,6 +393,36 @@ def test_clamped_gate_times_up_plus_one(device, dtype, tokens, ff, limit):
         close(ops.silu_mul(halves, dtype, activation="swish_clamped", limit=limit, alpha=1.702), want, dtype, scale=float(want.abs().max()))
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("tokens", [1, 5, 8, 40, 200, 700])
+@pytest.mark.parametrize("width,ff,limit", [(256, 512, 0.8), (512, 1024, 3.0), (128, 384, 0.3)])
+def test_the_feed_forward_part_in_every_form_of_its_gate_up_product(tokens, width, ff, limit):
+    """bfloat16: a few tokens take the weight-streaming kernel, many the tcgen05 product with the clamped gate in its
+    epilogue, the rest the product and the stand-alone kernel; all against the plain feed-forward."""
+    from lily_b200.csrc import ops
+    from lily_b200.engine.batch import Workspace
+    from lily_b200.parts.base import BuildContext, build_part
+    from lily_b200.parts.mlp import SwiGLUSpec
+
+    g = torch.Generator().manual_seed(tokens + ff)
+    w = {"f.gate": torch.randn(ff, width, generator=g) / math.sqrt(width) * 2.0, "f.up": torch.randn(ff, width, generator=g) / math.sqrt(width) * 2.0,
+         "f.down": torch.randn(width, ff, generator=g) / math.sqrt(ff)}
+    w = {k: v.bfloat16() for k, v in w.items()}
+    x = torch.randn(tokens, width, generator=g).bfloat16()
+    want = pk.feed_forward(x.float(), {"p.mlp." + k[2:]: v.float() for k, v in w.items()}, "p.mlp", limit)
+    ctx = BuildContext(device=torch.device("cuda"), dtype=torch.bfloat16, ops=ops)
+    part = build_part("feed_forward", SwiGLUSpec(width, ff, activation="swish_clamped", limit=limit, alpha=1.702,
+                                                 names=(("gate", "gate"), ("up", "up"), ("down", "down"))), "f", ctx)
+    part.load(lambda name: w[name].cuda())
+
+    class Step:
+        workspace = Workspace("cuda")
+    out = part.forward(x.cuda(), Step())
+    out = out.sum(0) if out.dim() == 3 else out              # a few tokens: the down product comes as partial sums
+    close(out, want, torch.bfloat16, scale=float(want.abs().max()))
+    assert ops.gemm_tc_status() == 0
+
+
 @pytest.mark.parametrize("device", DEVICES)
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("tokens,width", [(3, 48), (70, 256), (2, 1024), (9, 4096), (130, 200), (5, 50)])

@@ -10,7 +10,7 @@ alternate as [delta, attention + feed-forward, mamba1, attention + feed-forward]
 with keys and values of the size's head width (its state is heads x head x head float32 a request); the selective scan
 has 2 x width channels of 16 state entries and a step rank of width / 16; the attention has the size's heads with keys
 and values of the head width, biases, q/k norm, half of the head rotated, the sink and mixed heads (the kernel table also
-has the attention with values of 48 columns, a shape the CUDA-core kernels take); the
+has the attention with values of 40 columns, a shape the CUDA-core kernels take); the
 feed-forward has the dense layer's width.
 Timing as in ``design_bench``: device time by CUDA events after warm-up, weights and caches larger than L2, kernels
 over rotated inputs replayed from a graph.
@@ -208,10 +208,9 @@ def kernel_table(z: dict, tokens: int, batch: int, context: int, reps: int = 30,
     decode("attention_decode (sink, values of all kv heads)", "attention_decode", dv, sink=True, all_values=True)
     decode("attention_decode (sink alone)", "attention_decode", dv, sink=True)
     decode("attention_decode (dense heads)", "-", dd)
-    if dv != 48:
-        # a value size of its own (keys 128 / values 48 a head): the CUDA-core kernels take these shapes
-        prefill("attention_prefill (sink, all kv heads; values of 48: CUDA cores)", "attention_prefill", 48, sink=True, all_values=True)
-        decode("attention_decode (sink, all kv heads; values of 48: CUDA cores)", "attention_decode", 48, sink=True, all_values=True)
+    # a value size of its own (values of 40 columns a head beside keys of the head width): the CUDA-core kernels take these shapes
+    prefill("attention_prefill (sink, all kv heads; values of 40: CUDA cores)", "attention_prefill", 40, sink=True, all_values=True)
+    decode("attention_decode (sink, all kv heads; values of 40: CUDA cores)", "attention_decode", 40, sink=True, all_values=True)
     return rows
 
 

@@ -38,7 +38,7 @@ struct AttnArgs {
                               // keys [kv_heads, page_size, d] followed by its values [kv_heads, page_size, dv]
     int v_in_k;               // CUDA-core kernels: the values are the first dv columns of the key rows; a page holds keys only
     int keep_first;           // with a window: keys at positions below this stay visible whatever the distance
-    int v_shift;              // mma.sync kernels: a query head of kv head g reads the values of kv head (g + v_shift) % nkv (its
+    int v_shift;              // mma.sync and CUDA-core kernels: a query head of kv head g reads the values of kv head (g + v_shift) % nkv (its
                               // keys stay its own): nkv launches give every head's weights over every kv head's values
     int sink;                 // CUDA-core and mma.sync kernels: the softmax's denominator holds one more unit (a key of score 0 without a value)
     int v_all;                // CUDA-core kernels: a query head is weighted over the values of every kv head, not only its own:

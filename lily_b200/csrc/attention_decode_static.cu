@@ -6,7 +6,7 @@
 
 // The existing launchers this entry point drives (attention_simt.cu, attention_mma.cu).
 extern "C" int lily_attention_decode_simt(const void*, const void*, void*, const int*, int, const int*, float*, int, int,
-                                          int, int, int, int, int, float, int, float, int, int, int, cudaStream_t);
+                                          int, int, int, int, int, float, int, float, int, int, int, int, cudaStream_t);
 extern "C" int lily_attention_decode_mma(const void*, const void*, void*, const int*, int, const int*, float*, int, int,
                                          int, int, int, int, int, float, int, float, int, int, int, cudaStream_t);
 extern "C" int lily_attention_mma_supports(int);
@@ -74,5 +74,5 @@ LILY_API int lily_attention_decode_static(const void* q, const void* kv, void* o
                                          d, page_size, window, scale, 0, 0.f, 0, 0, 0, stream);
     }
     return lily_attention_decode_simt(q, kv, out, block_table, bt_stride, seq_lens, scratch, requests, splits, nq, nkv,
-                                      d, page_size, window, scale, dtype, 0.f, 0, 0, 0, stream);
+                                      d, page_size, window, scale, dtype, 0.f, 0, 0, 0, 0, stream);
 }

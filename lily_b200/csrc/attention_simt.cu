@@ -10,7 +10,8 @@
 // `sink`: a row's running (max, sum) start at (0, 1), a key of score 0 that has no value, so the weights are
 // exp(s_j) / (1 + sum exp(s_j)).  `v_all`: a query head's weights meet the values of every kv head at once (a value row
 // of nkv * dv columns gathered from the heads' tiles of the page), for callers that mix the heads' weights afterwards:
-// sum_g T[h][g] (P_g V_c) = (sum_g T[h][g] P_g) V_c.
+// sum_g T[h][g] (P_g V_c) = (sum_g T[h][g] P_g) V_c.  `v_shift`: instead, a query head of kv head g reads the values of kv head
+// (g + v_shift) % nkv, so that nkv launches give the same sums as planes (more than 512 value columns a row).
 //
 //  * prefill: grid (query tiles, query heads).  A tile is up to 32 consecutive new tokens of one
 //    request; their keys are the request's cached prefix and the new tokens up to each query
@@ -138,7 +139,7 @@ attention_simt_kernel(const AttnArgs a) {
                 const int page = table[kpos / a.page_size];
                 const T* base = kv + (size_t)page * page_stride;
                 const T* ksrc = base + (size_t)kvh * khead + (size_t)(kpos % a.page_size) * d;
-                const T* vsrc = base + (size_t)a.nkv * khead + (size_t)(a.v_all ? 0 : kvh) * vhead + (size_t)(kpos % a.page_size) * dv1;
+                const T* vsrc = base + (size_t)a.nkv * khead + (size_t)(a.v_all ? 0 : (kvh + a.v_shift) % a.nkv) * vhead + (size_t)(kpos % a.page_size) * dv1;
                 for (int c = lane; c < d; c += 32) Ks[j * (d + 1) + c] = to_float(ksrc[c]);
                 if (a.v_all)
                     for (int c = lane; c < dv; c += 32) Vs[j * dv + c] = to_float(vsrc[(size_t)(c / dv1) * vhead + c % dv1]);
@@ -375,8 +376,9 @@ LILY_API int lily_attention_prefill_simt(const void* q, const void* kv, void* ou
                                          int bt_stride, const int* cu_seqlens, const int* prefix_lens,
                                          const int* tile_req, const int* tile_start, int tiles, int nq, int nkv,
                                          int d, int page_size, int window, float scale, int dtype,
-                                         float softcap, int dv, int keep_first, int flags, cudaStream_t stream) {
+                                         float softcap, int dv, int keep_first, int flags, int v_shift, cudaStream_t stream) {
     if (tiles == 0) return 0;
+    LILY_REQUIRE(v_shift >= 0 && v_shift < nkv && !(v_shift && dv < 0), "attention_prefill: value heads shifted by %d of %d", v_shift, nkv);
     if (check_common("attention_prefill", nq, nkv, d, page_size, dv)) return 1;
     LILY_REQUIRE(nq <= 65535, "attention_prefill: %d query heads", nq);
     AttnArgs a{};
@@ -386,6 +388,7 @@ LILY_API int lily_attention_prefill_simt(const void* q, const void* kv, void* ou
     a.softcap = softcap; a.dv = dv > 0 ? dv : (dv < 0 ? -dv : d); a.v_in_k = dv < 0;
     a.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
     if (apply_flags("attention_prefill", a, flags)) return 1;
+    a.v_shift = v_shift;
     dim3 grid(tiles, nq);
     int rc = dtype == kBF16 ? launch<__nv_bfloat16, false>(a, grid, stream) : launch<float, false>(a, grid, stream);
     if (rc) return rc;
@@ -419,9 +422,10 @@ LILY_API size_t lily_attention_decode_scratch_floats(int requests, int nq, int d
 LILY_API int lily_attention_decode_simt(const void* q, const void* kv, void* out, const int* block_table,
                                         int bt_stride, const int* seq_lens, float* scratch, int requests,
                                         int splits, int nq, int nkv, int d, int page_size, int window,
-                                        float scale, int dtype, float softcap, int dv, int keep_first, int flags,
+                                        float scale, int dtype, float softcap, int dv, int keep_first, int flags, int v_shift,
                                         cudaStream_t stream) {
     if (requests == 0) return 0;
+    LILY_REQUIRE(v_shift >= 0 && v_shift < nkv && !(v_shift && dv < 0), "attention_decode: value heads shifted by %d of %d", v_shift, nkv);
     if (check_common("attention_decode", nq, nkv, d, page_size, dv)) return 1;
     const int d_one = dv > 0 ? dv : (dv < 0 ? -dv : d);
     const int d_out = (flags & kAllValues) ? nkv * d_one : d_one;
@@ -434,6 +438,7 @@ LILY_API int lily_attention_decode_simt(const void* q, const void* kv, void* out
     a.window = window; a.scale = scale; a.softcap = softcap; a.dv = d_one; a.v_in_k = dv < 0;
     a.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
     if (apply_flags("attention_decode", a, flags)) return 1;
+    a.v_shift = v_shift;
     a.part_o = scratch;
     a.part_ml = scratch ? scratch + (size_t)requests * nq * splits * d_out : nullptr;
     dim3 grid(requests, nkv * chunks, splits);

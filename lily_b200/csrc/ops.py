@@ -35,8 +35,8 @@ _SIGNATURES = {
     "lily_skinny_swiglu": [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _f, _vp],
     "lily_cast": [_vp, _i, _vp, _i, _sz, _vp],
     "lily_gemm_fp32": [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
-    "lily_attention_prefill_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _i, _i, _vp],
-    "lily_attention_decode_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _i, _i, _vp],
+    "lily_attention_prefill_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _i, _i, _i, _vp],
+    "lily_attention_decode_simt": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _f, _i, _i, _i, _i, _vp],
     "lily_attention_combine": [_vp, _vp, _i, _i, _i, _i, _i, _vp],
     "lily_attention_prefill_mma": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _i, _i, _i, _vp],
     "lily_attention_prefill_tc": [_vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _f, _i, _vp],
@@ -593,6 +593,8 @@ def prefill_tile_rows(dtype: torch.dtype = torch.float32, d: int = 0, page_size:
         return int(lib.lily_latent_attention_mma_tile_tokens(int(heads)))
     if (sink or all_values) and sink_on_tensor_cores(dtype, d, dv, values_in_keys, softcap):
         return int(lib.lily_attention_prefill_mma_rows())
+    if sink or all_values:
+        return int(lib.lily_attention_prefill_simt_rows())
     same = (dv is None or dv == d) and not values_in_keys and not sink and not all_values      # those run on CUDA cores
     if same and uses_tcgen05_attention(dtype, d, page_size, new_tokens):
         return int(lib.lily_attention_prefill_tc_rows())
@@ -639,7 +641,17 @@ def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torc
                   int(keep_first or 0) if window else 0, int(bool(sink)), shift, _stream())
         return
     if planes:
-        raise KernelError("attention_prefill: planes of sums are the mma.sync kernels' (bfloat16, one head size for keys and values)")
+        # the CUDA-core kernel, one launch a kv head with the value heads shifted
+        if tuple(out.shape) != (nkv, q.shape[0], nq * int(dv or d)) or values_in_keys:
+            raise KernelError(f"attention_prefill: planes of sums are [{nkv}, tokens, nq * dv]")
+        if (tile_rows or 0) not in (0, int(library().lily_attention_prefill_simt_rows())):
+            raise KernelError("attention_prefill: planes on the CUDA-core kernel come in its own tiles")
+        for shift in range(nkv):
+            _call("lily_attention_prefill_simt", _p(q), _p(kv_layer), out[shift].data_ptr(), _i32(block_table, "block_table"),
+                  block_table.shape[-1], _i32(cu_seqlens, "cu_seqlens"), _i32(prefix_lens, "prefix_lens"), _i32(tile_req, "tile_req"),
+                  _i32(tile_start, "tile_start"), tile_req.numel(), nq, nkv, d, page_size, int(window or 0), float(scale), _dt(q),
+                  float(softcap or 0.0), int(dv or d), int(keep_first or 0) if window else 0, 1 if sink else 0, shift, _stream())
+        return
     common = (_p(q), _p(kv_layer), _p(out), _i32(block_table, "block_table"), block_table.shape[-1],
               _i32(cu_seqlens, "cu_seqlens"), _i32(prefix_lens, "prefix_lens"), _i32(tile_req, "tile_req"),
               _i32(tile_start, "tile_start"), tile_req.numel(), nq, nkv, d, page_size, int(window or 0), float(scale))
@@ -668,9 +680,10 @@ def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torc
     elif tensor_cores:
         _call("lily_attention_prefill_mma", *common, cap, keep_first, 0, 0, _stream())
     else:
-        _call("lily_attention_prefill_simt", *common, _dt(q), cap, -dv if values_in_keys else dv, keep_first, flags, _stream())
+        _call("lily_attention_prefill_simt", *common, _dt(q), cap, -dv if values_in_keys else dv, keep_first, flags, 0, _stream())
 
 
+ALL_VALUES_COLUMNS = 512       # value columns a query row of the CUDA-core kernels gathers in one launch
 _SIMT_SINK = os.environ.get("LILY_B200_SINK_ATTENTION", "") == "simt"
 
 
@@ -681,13 +694,20 @@ def sink_on_tensor_cores(dtype: torch.dtype, d: int, dv: Optional[int] = None, v
     return (not _SIMT_SINK and not values_in_keys and int(dv or d) == d and uses_tensor_cores(dtype, d))
 
 
+def all_values_in_planes(dtype: torch.dtype, nkv: int, d: int, dv: Optional[int] = None) -> bool:
+    """Whether attention over the values of all kv heads runs as one launch a kv head (``all_values_sums`` then gives
+    planes): on the mma.sync kernels, and on the CUDA-core kernels when a row of ``nkv * dv`` columns would pass 512."""
+    return sink_on_tensor_cores(dtype, d, dv) or nkv * int(dv or d) > ALL_VALUES_COLUMNS
+
+
 def all_values_sums(dtype: torch.dtype, tokens: int, nq: int, nkv: int, d: int, dv: Optional[int], device) -> torch.Tensor:
     """The tensor that ``attention_prefill`` / ``attention_decode`` with ``all_values`` fill and ``head_mix`` reads.  On
     the CUDA-core kernels float32 [tokens, nq * nkv * dv]: a query head's row holds its weights' sums over every kv
-    head's values.  On the mma.sync kernels ``nkv`` planes [nkv, tokens, nq * dv] in ``dtype``: plane s holds, for a
-    query head of kv head g, the sums over the values of kv head (g + s) % nkv (one launch a plane)."""
+    head's values.  On the mma.sync kernels, and on the CUDA-core kernels when such a row would pass their 512 columns,
+    ``nkv`` planes [nkv, tokens, nq * dv] in ``dtype``: plane s holds, for a query head of kv head g, the sums over the
+    values of kv head (g + s) % nkv (one launch a plane)."""
     dv = int(dv or d)
-    if sink_on_tensor_cores(dtype, d, dv):
+    if all_values_in_planes(dtype, nkv, d, dv):
         return torch.empty((nkv, tokens, nq * dv), dtype=dtype, device=device)
     return torch.empty((tokens, nq * nkv * dv), dtype=torch.float32, device=device)
 
@@ -730,9 +750,9 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
     cap = float(softcap or 0.0)
     flags = _attention_flags(sink, all_values, values_in_keys, nkv, dv, out, requests * nq)
     on_tc = bool(flags) and sink_on_tensor_cores(q.dtype, d, dv, values_in_keys, softcap) and (planes or not all_values)
-    if planes and not on_tc:
-        raise KernelError("attention_decode: planes of sums are the mma.sync kernels' (bfloat16, one head size for keys and values)")
-    need = decode_scratch_floats(requests, nq, dv if on_tc else (nkv * dv if all_values else dv), splits)
+    if planes and values_in_keys:
+        raise KernelError("attention_decode: values that are columns of the key rows belong to one shared head")
+    need = decode_scratch_floats(requests, nq, dv if planes else (nkv * dv if all_values else dv), splits)
     if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
         raise KernelError(f"attention_decode: scratch of {need} float32 needed")
     common = (_p(q), _p(kv_layer), _p(out), _i32(block_table, "block_table"), block_table.shape[-1],
@@ -759,10 +779,13 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
     else:
         if stages:
             raise KernelError(f"attention_decode: {stages} stages are the tensor-core kernel's; {q.dtype}, head size {d} runs on CUDA cores")
-        _call("lily_attention_decode_simt", *common, _dt(q), cap, -dv if values_in_keys else dv,
-              int(keep_first or 0) if window else 0, flags, _stream())
-        if splits > 1:
-            launches["count"] += 1          # the combine kernel, launched inside
+        for shift in range(nkv if planes else 1):
+            _call("lily_attention_decode_simt", _p(q), _p(kv_layer), out[shift].data_ptr() if planes else _p(out),
+                  _i32(block_table, "block_table"), block_table.shape[-1], _i32(seq_lens, "seq_lens"), _p(scratch), requests, splits,
+                  nq, nkv, d, page_size, int(window or 0), float(scale), _dt(q), cap, -dv if values_in_keys else dv,
+                  int(keep_first or 0) if window else 0, (1 if sink else 0) if planes else flags, shift, _stream())
+            if splits > 1:
+                launches["count"] += 1          # the combine kernel, launched inside
 
 
 def sm_count() -> int:

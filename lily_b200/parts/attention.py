@@ -220,7 +220,9 @@ class Attention(Mixer):
             tiled = dict(tiled, sink=s.sink, all_values=s.talk)
             if not ops.sink_on_tensor_cores(dtype, s.head_dim, s.value_dim):
                 # options of the CUDA-core kernels; with mixed heads a query head's output row spans all kv heads' values
-                sized = dict(sized, cuda_cores=True, dv=s.num_kv_heads * s.value_dim if s.talk else s.value_dim)
+                # (unless those come as a plane a kv head)
+                wide = s.talk and not ops.all_values_in_planes(dtype, s.num_kv_heads, s.head_dim, s.value_dim)
+                sized = dict(sized, cuda_cores=True, dv=s.num_kv_heads * s.value_dim if wide else s.value_dim)
             else:
                 sized = dict(sized, fusable=False)      # one launch a kv head of the mma.sync kernel, queries prepared ahead
 

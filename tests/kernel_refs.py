@@ -685,6 +685,10 @@ def sink_on_tensor_cores(dtype, d, dv=None, values_in_keys=False, softcap=None):
     return False
 
 
+def all_values_in_planes(dtype, nkv, d, dv=None):
+    return False
+
+
 def all_values_sums(dtype, tokens, nq, nkv, d, dv, device):
     return torch.empty((tokens, nq * nkv * (dv or d)), dtype=torch.float32, device=device)
 

@@ -61,9 +61,9 @@ SHARP = {"architecture": "Kinanex", "vocab": 97, "width": 32, "norm": {"eps": 1e
 WIDE = {"architecture": "Kinanex", "vocab": 257, "width": 128, "norm": {"eps": 1e-6},
         "layers": [delta(heads=4, kv_heads=2, dim=64, vdim=32, conv=4, ff=None),
                    attention(heads=4, kv_heads=1, dim=64, vdim=64, scale=0.15, rot_dims=32, base=10000.0,
-                             scaling={"factor": 8.0, "low": 1.0, "high": 4.0, "original": 64}, ff=192, limit=1.0),
+                             scaling={"factor": 6.0, "low": 1.0, "high": 3.0, "original": 64}, ff=192, limit=1.5),
                    mamba(inner=192, state=16, dt_rank=8, conv=3, ff=None),
-                   delta(heads=2, kv_heads=2, dim=128, vdim=48, conv=3, ff=128, limit=3.0),
+                   delta(heads=2, kv_heads=2, dim=128, vdim=40, conv=3, ff=128, limit=3.0),
                    attention(heads=8, kv_heads=4, dim=32, vdim=16, scale=0.2, v_mix=False, rot_dims=32, ff=None),
                    attention(heads=4, kv_heads=1, dim=64, vdim=64, scale=0.15, rot_dims=64, ff=128, limit=0.5)]}
 

@@ -68,6 +68,21 @@ WIDE = {"architecture": "Kinanex", "vocab": 257, "width": 128, "norm": {"eps": 1
                    attention(heads=4, kv_heads=1, dim=64, vdim=64, scale=0.15, rot_dims=64, ff=128, limit=0.5)]}
 
 
+# Values that other configurations happen to make equal or 1: one head, as many kv heads as heads, values wider than
+# keys, a single tap and a single state entry, a step rank above the state size, a recurrence first and an attention last.
+ODD = {"architecture": "Kinanex", "vocab": 53, "width": 40, "norm": {"eps": 1e-4}, "logit_scale": 3.0,
+       "layers": [mamba(inner=24, state=1, dt_rank=7, conv=1, ff=None),
+                  delta(heads=1, kv_heads=1, dim=40, vdim=72, conv=4, ff=48, limit=1.2),
+                  attention(heads=3, kv_heads=3, dim=20, vdim=28, rot_dims=20, scale=0.25, ff=None),
+                  delta(heads=6, kv_heads=1, dim=8, vdim=4, conv=2, ff=None),
+                  attention(heads=5, kv_heads=1, dim=16, vdim=16, v_mix=False, rot_dims=6, scale=0.3, ff=16, limit=0.4),
+                  attention(heads=3, kv_heads=3, dim=12, vdim=28, rot_dims=0, scale=0.5, ff=None)]}
+
+# No attention at all: a model without a paged cache.
+RECURRENT = {"architecture": "Kinanex", "vocab": 61, "width": 32, "norm": {"eps": 1e-6}, "logit_scale": 1.0,
+             "layers": [delta(heads=2, kv_heads=2, dim=16, vdim=16, conv=3, ff=32), mamba(inner=48, state=8, dt_rank=4, conv=3, ff=None)]}
+
+
 def shapes(cfg: dict) -> Dict[str, tuple]:
     w = cfg["width"]
     out = {"embed": (cfg["vocab"], w), "embed.norm": (w,), "final.norm": (w,)}

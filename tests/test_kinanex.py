@@ -17,7 +17,7 @@ from lily_b200.config.model_config import ConfigError
 from lily_b200.engine.batch import StepEntry
 
 DEVICES = ["cpu", pytest.param("cuda", marks=pytest.mark.gpu)]
-CONFIGS = {"varied": km.VARIED, "sharp": km.SHARP, "wide": km.WIDE}
+CONFIGS = {"varied": km.VARIED, "sharp": km.SHARP, "wide": km.WIDE, "odd": km.ODD, "recurrent": km.RECURRENT}
 
 
 def plain_logits(cfg, weights, ids, dtype="float32"):

@@ -108,7 +108,10 @@ def kernel_table(z: dict, tokens: int, batch: int, context: int, reps: int = 30,
         zs = [rnd(n, 2 * inner).to(dt) for _ in range(copies)]
         a_mat, d_skip = -torch.rand(inner, ns, device=dev, generator=g) - 0.1, rnd(inner)
         sstates = [torch.zeros(reqs + 1, inner * ns, device=dev) for _ in range(copies)]
-        add("selective_scan", "ssd_scan", [lambda x=x, lo=lo, st=st, zz=zz, s=s: ops.selective_scan(x, lo, rank, st, zz, inner, a_mat, d_skip, s, cu, slots, reqs)
+        cplan = ops.scan_plan([per] * reqs, dev, inner * ns)                   # long portions run as chunks, as in the model
+        croom = torch.empty(max(1, ops.selective_workspace_floats(cplan, inner, ns)), device=dev)
+        add("selective_scan", "ssd_scan", [lambda x=x, lo=lo, st=st, zz=zz, s=s: ops.selective_scan(x, lo, rank, st, zz, inner, a_mat, d_skip, s, cu, slots, reqs,
+                                                                                                    plan=cplan, workspace=croom)
                                            for x, lo, st, zz, s in zip(xs, lows, steps, zs, sstates)],
             n * (inner * (2 + 4 + 2 + 2) + (rank + 2 * ns) * 2) + 2 * reqs * inner * ns * 4, 6.0 * n * inner * ns, fp32_tflops, shape=label)
         s_inner, s_state = z["s_heads"] * z["s_head"], z["state"]

@@ -50,7 +50,8 @@ _SIGNATURES = {
     "lily_add_normed_rmsnorm": [_vp, _vp, _i, _i, _sz, _vp, _f, _f, _vp, _i, _vp, _i, _vp, _i, _i, _f, _i, _i, _vp],
     "lily_head_mix": [_vp, _i, _i, _vp, _vp, _i, _i, _i, _i, _i, _vp],
     "lily_delta_rule": [_vp, _i, _i, _i, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _sz, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _f, _i, _vp],
-    "lily_selective_scan": [_vp, _vp, _i, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _vp, _sz, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp],
+    "lily_selective_scan": [_vp, _vp, _i, _i, _i, _vp, _vp, _i, _i, _vp, _vp, _vp, _sz, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _vp, _vp],
+    "lily_selective_combine": [_vp, _sz, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _i, _i, _vp],
     "lily_activation": [_vp, _i, _i, _sz, _vp, _i, _sz, _i, _vp],
     "lily_diff_prepare": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp],
     "lily_diff_combine": [_vp, _vp, _i, _i, _vp, _i, _i, _i, _i, _f, _f, _f, _i, _vp],
@@ -1692,15 +1693,29 @@ def selective_scan_max_state() -> int:
     return int(library().lily_selective_scan_max_state())
 
 
+def selective_workspace_floats(plan: Optional[ScanPlan], inner: int, n_state: int) -> int:
+    """Float32 scratch the chunks of ``plan`` need: a state and a sum of steps a chunk.  0 when the long portions are
+    better run in one piece each: the chunked form does the recurrence's work twice, which pays while the blocks of the
+    whole portions (16 channels a block) leave most of the device's warp slots empty (measured, 2,048 tokens of one
+    request, 16 state entries: 4,096 channels 564 -> 419 us in chunks, 8,192 channels 666 -> 816 us)."""
+    if plan is None or not plan.num_chunks:
+        return 0
+    if plan.num_long * -(-inner // 16) > 2.5 * sm_count():
+        return 0
+    return plan.num_chunks * inner * (n_state + 1)
+
+
 def selective_scan(x: torch.Tensor, low: torch.Tensor, b_col: int, step: torch.Tensor, proj: torch.Tensor, z_col: int,
                    a: torch.Tensor, d_skip: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor,
-                   requests: int) -> torch.Tensor:
+                   requests: int, plan: Optional[ScanPlan] = None, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The selective scan with a state vector per channel over each request's new tokens, from and to
     ``state[slot, :inner * n]`` (float32).  ``x`` [tokens, inner]: the convolved, activated inputs; ``low``
     [tokens, width]: B in the ``n`` columns from ``b_col``, C in the ``n`` after them; ``step`` float32 [tokens, inner]:
     the step projection with its bias, before softplus; the gate z in ``proj[:, z_col:z_col + inner]``; ``a`` float32
-    [inner, n] (negative); ``d_skip`` float32 [inner].  Returns ``(S . C + D x) * silu(z)`` in ``x``'s dtype."""
-    _dev(x, low, step, proj, a, d_skip, state, cu_seqlens, slots)
+    [inner, n] (negative); ``d_skip`` float32 [inner].  Returns ``(S . C + D x) * silu(z)`` in ``x``'s dtype.
+    With a ``plan`` (``scan_plan``) that has chunks and a ``workspace`` of ``selective_workspace_floats``, the long
+    portions run as chunks side by side (two passes and ``selective_combine`` between them), the others in one piece."""
+    _dev(x, low, step, proj, a, d_skip, state, cu_seqlens, slots, workspace)
     tokens, inner = x.shape
     n = a.shape[1]
     if step.dtype != torch.float32 or tuple(step.shape) != (tokens, inner) or a.dtype != torch.float32 or a.shape[0] != inner \
@@ -1709,7 +1724,23 @@ def selective_scan(x: torch.Tensor, low: torch.Tensor, b_col: int, step: torch.T
     if low.dtype != x.dtype or proj.dtype != x.dtype or b_col + 2 * n > low.shape[1] or z_col + inner > proj.shape[1]:
         raise KernelError("selective_scan: B, C or gate columns out of range, or dtypes differ")
     out = torch.empty((tokens, inner), dtype=x.dtype, device=x.device)
-    _call("lily_selective_scan", _p(x), _p(low), low.shape[1], int(b_col), int(b_col) + n, _p(step), _p(proj), proj.shape[1],
-          int(z_col), _p(a), _p(d_skip), _p(state), state.shape[1], _p(out), _i32(cu_seqlens, "cu_seqlens"),
-          _i32(slots, "slots"), int(requests), tokens, inner, n, _dt(x), _stream())
+    common = (_p(x), _p(low), low.shape[1], int(b_col), int(b_col) + n, _p(step), _p(proj), proj.shape[1], int(z_col), _p(a),
+              _p(d_skip), _p(state), state.shape[1], _p(out), _i32(cu_seqlens, "cu_seqlens"), _i32(slots, "slots"))
+    need = selective_workspace_floats(plan, inner, n)
+    if not need:
+        _call("lily_selective_scan", *common, int(requests), tokens, inner, n, _dt(x), None, None, None, 0, None, None, _stream())
+        return out
+    if workspace is None or workspace.dtype != torch.float32 or workspace.numel() < need:
+        raise KernelError(f"selective_scan: a float32 workspace of {need} entries needed")
+    ws_state = workspace.data_ptr()
+    ws_steps = ws_state + 4 * plan.num_chunks * inner * n
+    lists = (_i32(plan.chunk_req, "chunk_req"), _i32(plan.chunk_start, "chunk_start"), _i32(plan.chunk_len, "chunk_len"))
+    _call("lily_selective_scan", *common, plan.num_chunks, tokens, inner, n, _dt(x), *lists, 1, ws_state, ws_steps, _stream())
+    _call("lily_selective_combine", _p(state), state.shape[1], _i32(slots, "slots"), _i32(plan.long_req, "long_req"),
+          _i32(plan.long_first, "long_first"), _i32(plan.long_count, "long_count"), plan.num_long, _p(a), ws_state, ws_steps,
+          inner, n, _stream())
+    _call("lily_selective_scan", *common, plan.num_chunks, tokens, inner, n, _dt(x), *lists, 2, ws_state, ws_steps, _stream())
+    if plan.num_direct:
+        _call("lily_selective_scan", *common, plan.num_direct, tokens, inner, n, _dt(x), _i32(plan.direct, "direct"), None, None,
+              0, None, None, _stream())
     return out

@@ -11,6 +11,11 @@
 // next tile's inputs are loaded into registers while the current one is worked on.  The
 // step size, the decay, the state and the sums are float32 whatever the activation dtype.  State row of a slot:
 // [inner][state] (state fastest) at the row's start.
+//
+// A long portion is cut into chunks that run side by side (the recurrence is diagonal): a first pass runs every chunk
+// from a zero state and leaves its end state L_c and the sum of its steps in a workspace; `selective_combine` walks a
+// request's chunks in order, S <- exp(A sum_c dt) S + L_c, leaves in the workspace the state each chunk starts from
+// and writes the slot; a second pass runs every chunk from there and writes the outputs.
 #include "common.cuh"
 
 namespace lily {
@@ -35,6 +40,14 @@ struct SelectiveArgs {
     const int* cu_seqlens;
     const int* slots;
     int inner, n_state;
+    // the work of block x: request work_req[x] (null: request x), its tokens [work_start[x], + work_len[x]) (null: all)
+    const int* work_req;
+    const int* work_start;
+    const int* work_len;
+    int mode;                 // 0: from and to the slot; 1: chunk x from zero, end state and sum of steps to the workspace,
+                              // no outputs; 2: chunk x from the workspace's state, outputs, no state written
+    float* ws_state;          // [chunks][inner][n_state]
+    float* ws_steps;          // [chunks][inner]
 };
 
 // grid (requests, ceil(inner / SCAN_CHANNELS)), block SCAN_THREADS; n_state <= SL * NR
@@ -47,20 +60,23 @@ __global__ void __launch_bounds__(SCAN_THREADS) selective_scan_kernel(const Sele
     __shared__ float dts[SCAN_TOKENS][SCAN_CHANNELS], xs[SCAN_TOKENS][SCAN_CHANNELS], zs[SCAN_TOKENS][SCAN_CHANNELS],
         ys[SCAN_TOKENS][SCAN_CHANNELS];
     pdl_enter_small();
-    const int req = blockIdx.x, ch0 = blockIdx.y * SCAN_CHANNELS;
+    const int req = a.work_req ? a.work_req[blockIdx.x] : blockIdx.x, ch0 = blockIdx.y * SCAN_CHANNELS;
     const int l = threadIdx.x % SL, cg = threadIdx.x / SL;
     const int ch = ch0 + cg, inner = a.inner, ns = a.n_state;
     const bool ch_ok = ch < inner;
-    const int tok0 = a.cu_seqlens[req], len = a.cu_seqlens[req + 1] - tok0;
+    const int first = a.work_start ? a.work_start[blockIdx.x] : 0;
+    const int tok0 = a.cu_seqlens[req] + first, len = a.work_len ? a.work_len[blockIdx.x] : a.cu_seqlens[req + 1] - tok0;
     if (len <= 0) return;
-    float* st = a.state + (size_t)a.slots[req] * a.state_stride + (size_t)(ch_ok ? ch : 0) * ns;
-    float S[NR], A[NR];
+    const int mode = a.mode;
+    float* st = mode == 0 ? a.state + (size_t)a.slots[req] * a.state_stride + (size_t)(ch_ok ? ch : 0) * ns
+                          : a.ws_state + ((size_t)blockIdx.x * inner + (ch_ok ? ch : 0)) * ns;
+    float S[NR], A[NR], steps = 0.f;
 #pragma unroll
     for (int r = 0; r < NR; ++r) {
         const int n = l + SL * r;
         const bool ok = ch_ok && n < ns;
-        S[r] = ok ? st[n] : 0.f;
-        A[r] = ok ? a.A[(size_t)ch * ns + n] : 0.f;
+        S[r] = ok && mode != 1 ? st[n] : 0.f;
+        A[r] = ok ? a.A[(size_t)ch * ns + n] * 1.4426950408889634f : 0.f;      // in units of log2: the decay is one exp2 an entry
     }
     const float skip = ch_ok ? a.D[ch] : 0.f;
     const T* x = (const T*)a.x;
@@ -116,10 +132,11 @@ __global__ void __launch_bounds__(SCAN_THREADS) selective_scan_kernel(const Sele
 #pragma unroll 4
         for (int t = 0; t < n; ++t) {                 // the exponentials and the lane sums of neighbouring tokens overlap
             const float dt = dts[t][cg], xv = xs[t][cg], dx = dt * xv;
+            steps += dt;
             float acc = 0.f;
 #pragma unroll
             for (int r = 0; r < NR; ++r) {
-                S[r] = fmaf(expf(dt * A[r]), S[r], dx * Bs[t][l + SL * r]);
+                S[r] = fmaf(exp2f(dt * A[r]), S[r], dx * Bs[t][l + SL * r]);
                 acc = fmaf(S[r], Cs[t][l + SL * r], acc);
             }
 #pragma unroll
@@ -130,18 +147,42 @@ __global__ void __launch_bounds__(SCAN_THREADS) selective_scan_kernel(const Sele
             }
         }
         __syncthreads();
-        for (int e = threadIdx.x; e < n * SCAN_CHANNELS; e += SCAN_THREADS) {
-            const int t = e / SCAN_CHANNELS, c = e % SCAN_CHANNELS;
-            if (ch0 + c < inner) out[(size_t)(tok0 + t0 + t) * inner + ch0 + c] = from_float<T>(ys[t][c]);
-        }
+        if (mode != 1)
+            for (int e = threadIdx.x; e < n * SCAN_CHANNELS; e += SCAN_THREADS) {
+                const int t = e / SCAN_CHANNELS, c = e % SCAN_CHANNELS;
+                if (ch0 + c < inner) out[(size_t)(tok0 + t0 + t) * inner + ch0 + c] = from_float<T>(ys[t][c]);
+            }
     }
-    if (ch_ok) {
+    if (ch_ok && mode != 2) {
 #pragma unroll
         for (int r = 0; r < NR; ++r) {
             const int n = l + SL * r;
             if (n < ns) st[n] = S[r];
         }
+        if (mode == 1 && l == 0) a.ws_steps[(size_t)blockIdx.x * inner + ch] = steps;
     }
+}
+
+// grid (long requests, ceil(inner * n_state / 256)): a thread an entry of a request's state, its chunks in order.
+__global__ void selective_combine_kernel(float* __restrict__ state, size_t state_stride, const int* __restrict__ slots,
+                                         const int* __restrict__ long_req, const int* __restrict__ long_first,
+                                         const int* __restrict__ long_count, const float* __restrict__ A,
+                                         float* __restrict__ ws_state, const float* __restrict__ ws_steps, int inner, int ns) {
+    pdl_enter_small();
+    const int e = blockIdx.y * blockDim.x + threadIdx.x;
+    if (e >= inner * ns) return;
+    const int ch = e / ns;
+    float* slot = state + (size_t)slots[long_req[blockIdx.x]] * state_stride + e;
+    const float rate = A[e];
+    float S = *slot;
+    const int c0 = long_first[blockIdx.x], c1 = c0 + long_count[blockIdx.x];
+    for (int c = c0; c < c1; ++c) {
+        float* at = ws_state + (size_t)c * inner * ns + e;
+        const float own = *at;
+        *at = S;                                                     // what chunk c starts from
+        S = fmaf(expf(rate * ws_steps[(size_t)c * inner + ch]), S, own);
+    }
+    *slot = S;
 }
 
 }  // namespace lily
@@ -153,8 +194,12 @@ LILY_API int lily_selective_scan_max_state() { return SL * 32; }
 LILY_API int lily_selective_scan(const void* x, const void* low, int low_stride, int b_col, int c_col, const float* step,
                                  const void* z, int z_stride, int z_col, const float* A, const float* D, float* state,
                                  size_t state_stride, void* out, const int* cu_seqlens, const int* slots, int requests, int tokens,
-                                 int inner, int n_state, int dtype, cudaStream_t stream) {
+                                 int inner, int n_state, int dtype, const int* work_req, const int* work_start,
+                                 const int* work_len, int mode, float* ws_state, float* ws_steps, cudaStream_t stream) {
+    // `requests`: the blocks along x (requests, or the entries of the work lists)
     if (requests == 0) return 0;
+    LILY_REQUIRE(mode >= 0 && mode <= 2 && (mode == 0 || (work_req && work_start && work_len && ws_state && ws_steps)),
+                 "selective_scan: chunks come with their lists and a workspace");
     LILY_REQUIRE(inner > 0 && n_state > 0 && n_state <= SL * 32, "selective_scan: %d channels of %d state entries (up to %d)", inner, n_state, SL * 32);
     LILY_REQUIRE((size_t)inner * n_state <= state_stride, "selective_scan: the state row is shorter than %d x %d", inner, n_state);
     LILY_REQUIRE((inner + SCAN_CHANNELS - 1) / SCAN_CHANNELS <= 65535, "selective_scan: %d channels", inner);
@@ -162,9 +207,10 @@ LILY_API int lily_selective_scan(const void* x, const void* low, int low_stride,
     a.x = x; a.low = low; a.low_stride = low_stride; a.b_col = b_col; a.c_col = c_col; a.step = step;
     a.z = z; a.z_stride = z_stride; a.z_col = z_col; a.A = A; a.D = D; a.state = state; a.state_stride = state_stride;
     a.out = out; a.cu_seqlens = cu_seqlens; a.slots = slots; a.inner = inner; a.n_state = n_state;
+    a.work_req = work_req; a.work_start = work_start; a.work_len = work_len; a.mode = mode; a.ws_state = ws_state; a.ws_steps = ws_steps;
     dim3 grid(requests, (inner + SCAN_CHANNELS - 1) / SCAN_CHANNELS), block(SCAN_THREADS);
     const int per = (n_state + SL - 1) / SL;
-    const bool ahead = tokens > requests;               // some request brings more than one token
+    const bool ahead = mode != 0 || tokens > requests;  // some request brings more than one token
 #define GO(NR)                                                                                                            \
     do {                                                                                                                  \
         if (dtype == kBF16) {                                                                                             \
@@ -183,5 +229,16 @@ LILY_API int lily_selective_scan(const void* x, const void* low, int low_stride,
     else GO(32);
 #undef GO
     LILY_CHECK_LAUNCH("selective_scan");
+    return 0;
+}
+
+LILY_API int lily_selective_combine(float* state, size_t state_stride, const int* slots, const int* long_req, const int* long_first,
+                                    const int* long_count, int num_long, const float* A, float* ws_state, const float* ws_steps,
+                                    int inner, int n_state, cudaStream_t stream) {
+    if (num_long == 0) return 0;
+    const int entries = inner * n_state;
+    launch_pdl(selective_combine_kernel, dim3(num_long, (entries + 255) / 256), dim3(256), 0, stream, state, state_stride, slots,
+               long_req, long_first, long_count, A, ws_state, ws_steps, inner, n_state);
+    LILY_CHECK_LAUNCH("selective_combine");
     return 0;
 }

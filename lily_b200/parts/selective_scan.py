@@ -111,6 +111,13 @@ class SelectiveScan(Mixer):
                                   chunk_start, batch.cu_seqlens, batch.slots, chunk)
         low = ops.linear(xc, self.w_x)                                        # [tokens, dt | B | C]
         step = ops.linear(low, self.w_dt, self.dt_bias, out_dtype=torch.float32)
+        # long portions run as chunks side by side; the cut is planned once a step for layers of one state size
+        plan = batch.plan(("scan_plan", self.scan_floats),
+                          lambda b: ops.scan_plan(b.h_new_lens, b.token_ids.device, self.scan_floats))
+        need = ops.selective_workspace_floats(plan, s.inner, s.state)
+        room = batch.workspace.floats("selective_chunks", need) if need and batch.workspace is not None else None
+        if need and room is None:
+            plan = None                                    # no scratch to be had: every portion runs whole
         gated = ops.selective_scan(xc, low, s.dt_rank, step, proj, s.inner, self.a, self.d_skip, state, batch.cu_seqlens,
-                                   batch.slots, batch.num_requests)
+                                   batch.slots, batch.num_requests, plan=plan, workspace=room)
         return ops.linear_auto(gated, self.w_o)

@@ -736,7 +736,11 @@ def selective_scan_max_state():
     return 256
 
 
-def selective_scan(x, low, b_col, step, proj, z_col, a, d_skip, state, cu_seqlens, slots, requests):
+def selective_workspace_floats(plan, inner, n_state):
+    return 0
+
+
+def selective_scan(x, low, b_col, step, proj, z_col, a, d_skip, state, cu_seqlens, slots, requests, plan=None, workspace=None):
     tokens, inner = x.shape
     n = a.shape[1]
     xf, dt = x.float(), torch.nn.functional.softplus(step.float())

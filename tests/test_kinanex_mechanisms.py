@@ -374,6 +374,46 @@ def test_selective_scan_whole_in_portions_and_in_slots_that_change_hands(device,
     assert float((state[:, -3:] - 7.0).abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("inner,state_n,rank", [(40, 6, 5), (192, 16, 8), (33, 32, 3)])
+def test_selective_scan_long_portions_in_chunks_side_by_side(device, dtype, inner, state_n, rank):
+    """One step with a portion of 700 tokens and one of 450 (both cut into chunks that run side by side and are joined
+    in order), one of 50 and a single token (each in one piece), all continuing from states that an earlier step left."""
+    if device == "cpu" and dtype == torch.bfloat16:
+        pytest.skip("the plain statements are checked in float32")
+    ops = ops_for(device)
+    g = torch.Generator().manual_seed(inner)
+    before, lens = [30, 0, 7, 90], [700, 450, 50, 1]
+    a_log = torch.log(torch.linspace(0.05, 2.0, state_n)).expand(inner, state_n) + 0.3 * torch.randn(inner, state_n, generator=g)
+    d_skip = 1.0 + 0.2 * torch.randn(inner, generator=g)
+    data = []
+    for n in [b + m for b, m in zip(before, lens)]:
+        x, low = torch.randn(n, inner, generator=g).to(dtype), torch.randn(n, rank + 2 * state_n, generator=g).to(dtype)
+        step, proj = torch.randn(n, inner, generator=g) - 1.0, torch.randn(n, 2 * inner, generator=g).to(dtype)
+        data.append((x, low, step, proj))
+    want = [plain_scan(x, low, rank, step, proj[:, inner:], a_log, d_skip) for x, low, step, proj in data]
+    a = (-torch.exp(a_log)).contiguous().to(device)
+    state = torch.zeros((6, inner * state_n), dtype=torch.float32, device=device)
+    slots = i32([5, 2, 1, 3], device)
+    for part, (lo, ns) in enumerate((([0] * 4, before), (before, lens))):
+        live = [r for r in range(4) if ns[r]]
+        cat = lambda j: torch.cat([data[r][j][lo[r]:lo[r] + ns[r]] for r in live]).to(device)
+        cu = i32([0] + torch.tensor([ns[r] for r in live]).cumsum(0).tolist(), device)
+        plan = ops.scan_plan([ns[r] for r in live], device, inner * state_n)
+        need = ops.selective_workspace_floats(plan, inner, state_n)
+        if device == "cuda" and part == 1:
+            assert plan.num_chunks == 6 + 4 and plan.num_direct == 2 and need > 0
+        room = torch.empty(max(need, 1), dtype=torch.float32, device=device)
+        y = ops.selective_scan(cat(0), cat(1), rank, cat(2), cat(3), inner, a, d_skip.to(device), state, cu,
+                               slots[torch.tensor(live)].contiguous(), len(live), plan=plan, workspace=room)
+        if part == 1:
+            at = 0
+            for r in live:
+                close(y[at:at + ns[r]], want[r][lo[r]:], dtype, scale=float(want[r].abs().max()))
+                at += ns[r]
+
+
 # ------------------------------------------------------------------ feed-forward, layer scale, frequencies
 
 @pytest.mark.parametrize("device", DEVICES)

@@ -155,11 +155,11 @@ def kernel_table(z: dict, tokens: int, batch: int, context: int, reps: int = 30,
         add("qk_norm_rope_write (like)", "-",
             [lambda x=x, c=c: ops.qk_norm_rope_write(x, qg, kg, 1e-6, cos, sin, positions, token_req, table, c, nq, nkv, dd, dd // 2, page, dv=dv)
              for x, c in zip(aqkv, caches)], n * (cols * 2 + nq * dd * 2 + nkv * (dd + dv) * 2), shape=label)
-        sized = {} if dv == dd else {"dv": dv}
-        sums = [rnd(n, nq * nkv * dv) for _ in range(copies)]
+        # the sums in the layout the attention leaves them in for these sizes (planes a kv head, or wide float32 rows)
+        sums = [ops.all_values_sums(dt, n, nq, nkv, dd, dv, dev).normal_() for _ in range(copies)]
         mix = torch.eye(nq, device=dev) + rnd(nq, nq) / 8
-        add("head_mix", "sigmoid_gate", [lambda s=s: ops.head_mix(s, mix, nq, nkv, dv, dt) for s in sums], n * nq * dv * (nkv * 4 + 2),
-            2.0 * n * nq * nq * dv, fp32_tflops, shape=label)
+        add("head_mix", "sigmoid_gate", [lambda s=s: ops.head_mix(s, mix, nq, nkv, dv, dt) for s in sums],
+            n * nq * dv * (nkv * sums[0].element_size() + 2), 2.0 * n * nq * nq * dv, fp32_tflops, shape=label)
 
     # ---- attention: the sink and the values of all kv heads, beside the same kernel without them and the dense heads
     def prefill(name, like, d_v, **how):

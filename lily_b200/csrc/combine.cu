@@ -73,12 +73,14 @@ __global__ void head_mix_kernel(const IN* __restrict__ in, int planes, size_t pl
         float acc = 0.f;
         if (planes) {
             const IN* row = in + (size_t)blockIdx.x * nq * dv + c;
+#pragma unroll 4
             for (int g = 0; g < nq; ++g) {
                 const int s = (own - g / group + nkv) % nkv;               // the plane in which head g looked at kv head `own`
                 acc = fmaf(mix_s[h * nq + g], to_float(row[(size_t)s * plane_stride + (size_t)g * dv]), acc);
             }
         } else {
             const IN* src = in + (size_t)blockIdx.x * nq * nkv * dv + (size_t)own * dv + c;
+#pragma unroll 4
             for (int g = 0; g < nq; ++g) acc = fmaf(mix_s[h * nq + g], to_float(src[(size_t)g * nkv * dv]), acc);
         }
         out[(size_t)blockIdx.x * nq * dv + e] = from_float<T>(acc);

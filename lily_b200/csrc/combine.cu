@@ -59,32 +59,60 @@ __global__ void sigmoid_gate_bf16x8_kernel(__nv_bfloat16* __restrict__ out, cons
 // its weights' sums over the values of every kv head; head h takes the sums over its own kv head's values from all query
 // heads.  Two layouts of `in`: rows [tokens][nq][nkv][dv] (float32, the CUDA-core attention kernel's), or planes
 // [nkv][tokens][nq][dv] where plane s holds, for a head of kv head g, the sums over kv head (g + s) % nkv (one launch of
-// the mma.sync attention kernel a plane).  One block a token; the matrix [nq][nq] in shared memory.
-template <typename T, typename IN>
+// the mma.sync attention kernel a plane).  The matrix [nq][nq] in shared memory.
+// VEC neighbouring columns of one head a thread (8 from bfloat16 planes, 4 from float32, 16 bytes a load; 1 when the
+// value size does not divide); grid (tokens, blocks of columns).
+template <typename IN, int VEC>
+__device__ __forceinline__ void load_columns(const IN* __restrict__ src, float (&v)[VEC]) {
+    if constexpr (VEC == 8 && sizeof(IN) == 2) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(src);
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 f = __bfloat1622float2(p[k]);
+            v[2 * k] = f.x;
+            v[2 * k + 1] = f.y;
+        }
+    } else if constexpr (VEC == 4 && sizeof(IN) == 4) {
+        const float4 f = *reinterpret_cast<const float4*>(src);
+        v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    } else {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) v[k] = to_float(src[k]);
+    }
+}
+
+template <typename T, typename IN, int VEC>
 __global__ void head_mix_kernel(const IN* __restrict__ in, int planes, size_t plane_stride, const float* __restrict__ mix,
                                 T* __restrict__ out, int nq, int nkv, int dv) {
     extern __shared__ float mix_s[];
     pdl_enter_small();
     for (int i = threadIdx.x; i < nq * nq; i += blockDim.x) mix_s[i] = mix[i];
     __syncthreads();
-    const int group = nq / nkv;
-    for (int e = threadIdx.x; e < nq * dv; e += blockDim.x) {
-        const int h = e / dv, c = e % dv, own = h / group;
-        float acc = 0.f;
-        if (planes) {
-            const IN* row = in + (size_t)blockIdx.x * nq * dv + c;
+    const int e = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;      // this thread's first column among the token's nq * dv
+    if (e >= nq * dv) return;
+    const int group = nq / nkv, h = e / dv, c = e % dv, own = h / group;
+    const size_t tok = blockIdx.x;
+    float acc[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) acc[k] = 0.f;
+    for (int gk = 0; gk < nkv; ++gk) {
+        // the heads of kv head gk looked at kv head `own` in plane (own - gk) mod nkv
+        const IN* src = planes ? in + (size_t)((own - gk + nkv) % nkv) * plane_stride + (tok * nq + (size_t)gk * group) * dv + c
+                               : in + ((tok * nq + (size_t)gk * group) * nkv + own) * dv + c;
+        const size_t step = planes ? (size_t)dv : (size_t)nkv * dv;
+        const float* w = mix_s + h * nq + gk * group;
 #pragma unroll 4
-            for (int g = 0; g < nq; ++g) {
-                const int s = (own - g / group + nkv) % nkv;               // the plane in which head g looked at kv head `own`
-                acc = fmaf(mix_s[h * nq + g], to_float(row[(size_t)s * plane_stride + (size_t)g * dv]), acc);
-            }
-        } else {
-            const IN* src = in + (size_t)blockIdx.x * nq * nkv * dv + (size_t)own * dv + c;
-#pragma unroll 4
-            for (int g = 0; g < nq; ++g) acc = fmaf(mix_s[h * nq + g], to_float(src[(size_t)g * nkv * dv]), acc);
+        for (int gi = 0; gi < group; ++gi) {
+            float v[VEC];
+            load_columns<IN, VEC>(src + gi * step, v);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) acc[k] = fmaf(w[gi], v[k], acc[k]);
         }
-        out[(size_t)blockIdx.x * nq * dv + e] = from_float<T>(acc);
     }
+    T* dst = out + tok * nq * dv + e;
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) dst[k] = from_float<T>(acc[k]);
 }
 
 // One block a token.  VEC 4: four columns a thread and turn (the width a multiple of four, everything 16-byte aligned).
@@ -229,12 +257,20 @@ LILY_API int lily_head_mix(const void* in, int in_dtype, int planes, const float
     LILY_REQUIRE(planes || in_dtype == kF32, "head_mix: rows of sums over all kv heads are float32");
     const size_t smem = sizeof(float) * (size_t)nq * nq;
     LILY_REQUIRE(smem <= 48 * 1024, "head_mix: a matrix over %d heads does not fit shared memory", nq);
-    int threads = (nq * dv + 31) / 32 * 32;
-    threads = threads > 256 ? 256 : threads;
+    const bool aligned = ((uintptr_t)in & 15) == 0;
+    const int vec = in_dtype == kBF16 ? (dv % 8 == 0 && aligned ? 8 : 1) : (dv % 4 == 0 && aligned ? 4 : 1);
+    const int threads = tokens <= 64 ? 64 : 128;                     // few tokens: more blocks a token
     const size_t plane = (size_t)tokens * nq * dv;
-#define GO(T, IN) launch_pdl(head_mix_kernel<T, IN>, dim3(tokens), dim3(threads), smem, stream, (const IN*)in, planes, plane, mix, (T*)out, nq, nkv, dv)
-    if (out_dtype == kBF16) { if (in_dtype == kBF16) GO(__nv_bfloat16, __nv_bfloat16); else GO(__nv_bfloat16, float); }
-    else { if (in_dtype == kBF16) GO(float, __nv_bfloat16); else GO(float, float); }
+    dim3 grid(tokens, (nq * dv / vec + threads - 1) / threads);
+    LILY_REQUIRE(grid.y <= 65535, "head_mix: %d heads of %d value columns", nq, dv);
+#define GO(T, IN, V) launch_pdl(head_mix_kernel<T, IN, V>, grid, dim3(threads), smem, stream, (const IN*)in, planes, plane, mix, (T*)out, nq, nkv, dv)
+    if (out_dtype == kBF16) {
+        if (in_dtype == kBF16) { if (vec == 8) GO(__nv_bfloat16, __nv_bfloat16, 8); else GO(__nv_bfloat16, __nv_bfloat16, 1); }
+        else { if (vec == 4) GO(__nv_bfloat16, float, 4); else GO(__nv_bfloat16, float, 1); }
+    } else {
+        if (in_dtype == kBF16) { if (vec == 8) GO(float, __nv_bfloat16, 8); else GO(float, __nv_bfloat16, 1); }
+        else { if (vec == 4) GO(float, float, 4); else GO(float, float, 1); }
+    }
 #undef GO
     LILY_CHECK_LAUNCH("head_mix");
     return 0;

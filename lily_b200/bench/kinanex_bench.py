@@ -197,7 +197,8 @@ def kernel_table(z: dict, tokens: int, batch: int, context: int, reps: int = 30,
             out = ops.all_values_sums(dt, batch, nq, nkv, dd, d_v, dev) if how.get("all_values") else torch.empty((batch, nq * d_v), device=dev, dtype=dt)
             seq = torch.full((batch,), context, device=dev, dtype=torch.int32)
             on_cores = bool(how) and not ops.sink_on_tensor_cores(dt, dd, d_v)
-            plan = ops.plan_decode_attention(dt, batch, nq, nkv, dd, context, fusable=False,
+            seen = ops.all_values_decode_rows(dt, batch, nkv, dd, d_v) if how.get("all_values") else batch
+            plan = ops.plan_decode_attention(dt, seen, nq, nkv, dd, context, fusable=False,
                                              **({"dv": wide, "cuda_cores": True} if on_cores else sized))
             scratch = torch.empty(max(1, plan.scratch_floats), device=dev)
             fns.append(lambda q=q, cache=cache, tbl=tbl, out=out, seq=seq, scratch=scratch, plan=plan: ops.attention_decode(

@@ -40,6 +40,9 @@ struct AttnArgs {
     int keep_first;           // with a window: keys at positions below this stay visible whatever the distance
     int v_shift;              // mma.sync and CUDA-core kernels: a query head of kv head g reads the values of kv head (g + v_shift) % nkv (its
                               // keys stay its own): nkv launches give every head's weights over every kv head's values
+    int decode_rows;          // mma.sync decode kernel, > 0: every shift in one launch.  Block x works for request x % decode_rows
+                              // with the value heads shifted by x / decode_rows and writes row x of `out` and of the scratch
+                              // (planes of decode_rows rows: a step in which every request brings one token)
     int sink;                 // CUDA-core and mma.sync kernels: the softmax's denominator holds one more unit (a key of score 0 without a value)
     int v_all;                // CUDA-core kernels: a query head is weighted over the values of every kv head, not only its own:
                               // its output row is [nkv][dv] (the caller mixes heads afterwards); `dv` stays one head's size

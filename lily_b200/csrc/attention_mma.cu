@@ -142,9 +142,13 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
     const __nv_bfloat16* kv = (const __nv_bfloat16*)a.kv;
     const int group = a.nq / a.nkv;
 
-    int req, kvh, kbeg, kend, nrows, head0 = 0, tok0 = 0, pos0 = 0;
+    int req, kvh, kbeg, kend, nrows, head0 = 0, tok0 = 0, pos0 = 0, v_shift = a.v_shift;
     if (DECODE) {
         req = blockIdx.x;
+        if (a.decode_rows > 0) {                             // all shifts of the value heads in one launch
+            v_shift = req / a.decode_rows;
+            req -= v_shift * a.decode_rows;
+        }
         const int chunks = (group + 15) / 16;
         kvh = blockIdx.y / chunks;
         const int r0 = (blockIdx.y % chunks) * 16;
@@ -156,7 +160,7 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
         kend = min(seq, kbeg + per);
         nrows = min(16, group - r0);
         head0 = kvh * group + r0;
-        tok0 = req;
+        tok0 = blockIdx.x;                                   // the row written; the query's row is `req`
         pos0 = seq > 0 ? seq - 1 : 0;                        // an empty row (no position yet) reads table entry 0 at most
     } else {
         const int tile = gridDim.x - 1 - blockIdx.x;       // the tiles come ordered by the keys they see: longest first
@@ -187,7 +191,7 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
 
     const __nv_bfloat16* kv_head = kv + (size_t)kvh * head_stride;
     // the values lie nkv heads behind the keys; with v_shift, those of another kv head
-    const size_t v_off = (size_t)(a.nkv + (a.v_shift ? (kvh + a.v_shift) % a.nkv - kvh : 0)) * head_stride;
+    const size_t v_off = (size_t)(a.nkv + (v_shift ? (kvh + v_shift) % a.nkv - kvh : 0)) * head_stride;
     const int page_mask = (1 << page_shift) - 1;
     auto load_tile = [&](int t, int buf) {
         const int kb = tile_base(t), klim = tile_limit(t);
@@ -394,7 +398,7 @@ attention_mma_kernel(const AttnArgs a, const int page_shift) {
         const int r = i / CH, ch = i % CH;
         uint4 val = make_uint4(0, 0, 0, 0);
         if (r < nrows) {
-            const size_t tok = DECODE ? (size_t)tok0 : (size_t)tok0 + r;
+            const size_t tok = DECODE ? (size_t)req : (size_t)tok0 + r;
             const int head = DECODE ? head0 + r : head0;
             val = *reinterpret_cast<const uint4*>(q + (tok * a.nq + head) * D + ch * 8);
         }
@@ -901,8 +905,13 @@ LILY_API int lily_attention_decode_mma(const void* q, const void* kv, void* out,
                                        int nq, int nkv, int d, int page_size, int window, float scale, int stages,
                                        float softcap, int keep_first, int sink, int v_shift, cudaStream_t stream) {
     AttnArgs a{};
-    LILY_REQUIRE(nkv > 0 && v_shift >= 0 && v_shift < nkv, "attention_decode: value heads shifted by %d of %d", v_shift, nkv);
-    a.softcap = softcap; a.sink = sink; a.v_shift = v_shift;
+    // v_shift -1: every shift in one launch, nkv planes of `requests` rows in `out` (and as many rows of scratch)
+    LILY_REQUIRE(nkv > 0 && v_shift >= -1 && v_shift < nkv, "attention_decode: value heads shifted by %d of %d", v_shift, nkv);
+    a.softcap = softcap; a.sink = sink; a.v_shift = v_shift < 0 ? 0 : v_shift;
+    if (v_shift < 0) {
+        a.decode_rows = requests;
+        requests *= nkv;
+    }
     a.keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
     return decode_mma(a, q, kv, out, block_table, bt_stride, seq_lens, scratch, requests, splits, nq, nkv, d, page_size,
                       window, scale, stages, stream);

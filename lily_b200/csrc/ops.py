@@ -684,6 +684,7 @@ def attention_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torc
         _call("lily_attention_prefill_simt", *common, _dt(q), cap, -dv if values_in_keys else dv, keep_first, flags, 0, _stream())
 
 
+_MERGED_SHIFTS = os.environ.get("LILY_B200_MERGED_SHIFTS", "1") != "0"
 ALL_VALUES_COLUMNS = 512       # value columns a query row of the CUDA-core kernels gathers in one launch
 _SIMT_SINK = os.environ.get("LILY_B200_SINK_ATTENTION", "") == "simt"
 
@@ -693,6 +694,12 @@ def sink_on_tensor_cores(dtype: torch.dtype, d: int, dv: Optional[int] = None, v
     """Whether attention with a sink (and, in one launch a kv head, with the values of all kv heads) runs on the mma.sync
     kernels: bfloat16, keys and values of one head size that those kernels take; else the CUDA-core kernels."""
     return (not _SIMT_SINK and not values_in_keys and int(dv or d) == d and uses_tensor_cores(dtype, d))
+
+
+def all_values_decode_rows(dtype: torch.dtype, requests: int, nkv: int, d: int, dv: Optional[int] = None) -> int:
+    """The rows to plan the decode attention over the values of all kv heads for (``plan_decode_attention``): on the
+    mma.sync kernels a step of single tokens runs every shift of the value heads in one launch, ``nkv`` rows a request."""
+    return requests * nkv if sink_on_tensor_cores(dtype, d, dv) and _MERGED_SHIFTS else requests
 
 
 def all_values_in_planes(dtype: torch.dtype, nkv: int, d: int, dv: Optional[int] = None) -> bool:
@@ -753,7 +760,10 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
     on_tc = bool(flags) and sink_on_tensor_cores(q.dtype, d, dv, values_in_keys, softcap) and (planes or not all_values)
     if planes and values_in_keys:
         raise KernelError("attention_decode: values that are columns of the key rows belong to one shared head")
-    need = decode_scratch_floats(requests, nq, dv if planes else (nkv * dv if all_values else dv), splits)
+    # a step in which every request brings one token: all planes in one launch of the mma.sync kernel (block x works for
+    # request x % requests with the value heads shifted by x // requests), so a kv head's keys are fetched while they are in L2
+    merged = planes and on_tc and out.shape[1] == requests and nkv > 1 and _MERGED_SHIFTS
+    need = decode_scratch_floats(requests * nkv if merged else requests, nq, dv if planes else (nkv * dv if all_values else dv), splits)
     if need and (scratch is None or scratch.dtype != torch.float32 or scratch.numel() < need):
         raise KernelError(f"attention_decode: scratch of {need} float32 needed")
     common = (_p(q), _p(kv_layer), _p(out), _i32(block_table, "block_table"), block_table.shape[-1],
@@ -766,12 +776,13 @@ def attention_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_table: torch
         if splits > 1:
             _call("lily_attention_combine", _p(scratch), _p(out), requests, nq, dv, splits, _dt(q), _stream())
     elif on_tc:
-        for shift in range(nkv if planes else 1):
-            _call("lily_attention_decode_mma", _p(q), _p(kv_layer), out[shift].data_ptr() if planes else _p(out),
+        for shift in ([-1] if merged else range(nkv if planes else 1)):
+            _call("lily_attention_decode_mma", _p(q), _p(kv_layer), out[shift].data_ptr() if planes and not merged else _p(out),
                   _i32(block_table, "block_table"), block_table.shape[-1], _i32(seq_lens, "seq_lens"), _p(scratch), requests, splits,
                   nq, nkv, d, page_size, int(window or 0), float(scale), int(stages), cap, int(keep_first or 0) if window else 0,
                   int(bool(sink)), shift, _stream())
-            if splits > 1 and (stages or requests * nkv * -(-(nq // nkv) // 16) > decode_clusters(d, splits, nq // nkv)):
+            rows = requests * nkv if merged else requests
+            if splits > 1 and (stages or rows * nkv * -(-(nq // nkv) // 16) > decode_clusters(d, splits, nq // nkv)):
                 launches["count"] += 1
     elif dv == d and not values_in_keys and not flags and uses_tensor_cores(q.dtype, d):
         _call("lily_attention_decode_mma", *common, int(stages), cap, int(keep_first or 0) if window else 0, 0, 0, _stream())   # merges the splits itself (cluster, or combine behind)

@@ -228,9 +228,11 @@ class Attention(Mixer):
 
         def make(b):
             nd = b.num_decode
-            decode = ops.plan_decode_attention(dtype, nd, s.num_heads, s.num_kv_heads, s.head_dim, b.max_decode_len,
+            # the rows the decode kernel sees (with mixed heads it may run every kv head's values in one launch)
+            seen = ops.all_values_decode_rows(dtype, nd, s.num_kv_heads, s.head_dim, s.value_dim) if s.talk else nd
+            decode = ops.plan_decode_attention(dtype, seen, s.num_heads, s.num_kv_heads, s.head_dim, b.max_decode_len,
                                                even=b.decode_even, **sized)
-            if decode != ops.plan_decode_attention(dtype, nd, s.num_heads, s.num_kv_heads, s.head_dim, b.max_decode_len,
+            if decode != ops.plan_decode_attention(dtype, seen, s.num_heads, s.num_kv_heads, s.head_dim, b.max_decode_len,
                                                    even=not b.decode_even, **sized):
                 b.even_asked = True              # a captured step with this plan serves batches of this kind only
             if (s.conv_taps or s.v_norm or s.v_share) and decode.fused:

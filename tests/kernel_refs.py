@@ -685,6 +685,10 @@ def sink_on_tensor_cores(dtype, d, dv=None, values_in_keys=False, softcap=None):
     return False
 
 
+def all_values_decode_rows(dtype, requests, nkv, d, dv=None):
+    return requests
+
+
 def all_values_in_planes(dtype, nkv, d, dv=None):
     return False
 

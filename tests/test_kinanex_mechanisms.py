@@ -74,7 +74,8 @@ def run_attention(ops, device, dtype, q, k, v, talk, scale, page, cuts, sink=Tru
             o = torch.empty((n, heads * dv), dtype=dtype, device=device)
         if n == 1:
             if ops.sink_on_tensor_cores(dtype, d, dv):
-                plan = ops.plan_decode_attention(dtype, 1, heads, kvh, d, done + 1, fusable=False)
+                rows = ops.all_values_decode_rows(dtype, 1, kvh, d, dv) if talk is not None else 1
+                plan = ops.plan_decode_attention(dtype, rows, heads, kvh, d, done + 1, fusable=False)
             else:
                 plan = ops.plan_decode_attention(dtype, 1, heads, kvh, d, done + 1, dv=dv if o.dim() == 3 else wide, cuda_cores=True)
             scratch = torch.empty(max(1, plan.scratch_floats), dtype=torch.float32, device=device)
@@ -175,7 +176,7 @@ def test_the_sink_counts_once_however_the_keys_are_cut(device, splits, dtype, d,
     qq = ops.qk_norm_rope_write(qkv, None, None, 1e-6, None, None, i32(list(range(t)), device), i32([0] * t, device), table, cache,
                                 heads, kvh, d, 0, page, **sized)
     o = ops.all_values_sums(dtype, 1, heads, kvh, d, dv, device)
-    scratch = torch.empty(heads * splits * (kvh * dv + 2), dtype=torch.float32, device=device)
+    scratch = torch.empty(heads * splits * kvh * (dv + 2), dtype=torch.float32, device=device)
     ops.attention_decode(qq[-1:].contiguous(), cache, table, i32([t], device), o, scratch, splits, heads, kvh, d, page, 0.2, None,
                          sink=True, all_values=True, **sized)
     got = ops.head_mix(o, talk.to(device), heads, kvh, dv, torch.float32)
